@@ -1,5 +1,5 @@
 """Device memory of the cache: for every run of a layer that keeps a cache, key and value
-pages `[pages, kv_heads, page_size, head_dim]` in its group's page space, and for every
+pages `[pages, kv_heads, page_size, head_dim]` (values: their own head size where a mixer states one) in its group's page space, and for every
 mixer with a per-request state an array `[slots, *shape]`.  The reference keeps two tensors
 `[pages, page_size, kv_heads, head_dim]` per layer (crates/models/src/model.rs:96-120); here
 one head's rows of a page are contiguous, so a kernel reads a page of one head as one block."""
@@ -40,7 +40,7 @@ def bytes_per_page(needs: list[KVNeed | None], group_of: list[int], group: int, 
                    element_size: int) -> int:
     """Bytes that one page of a group takes over all the layers of the group
     (reference: `kv_bytes_per_page`, crates/models/src/model.rs:28-42)."""
-    return sum(2 * n.kv_heads * n.head_dim * page_size * element_size
+    return sum(n.kv_heads * (n.head_dim + n.v_head_dim) * page_size * element_size
                for n, g in zip(needs, group_of) if n is not None and g == group)
 
 
@@ -53,7 +53,7 @@ class CacheStorage:
             if need is not None:
                 shape = (groups[g].num_pages, need.kv_heads, runtime.page_size, need.head_dim)
                 entry.k = torch.zeros(shape, dtype=runtime.dtype, device=runtime.device)
-                entry.v = torch.zeros(shape, dtype=runtime.dtype, device=runtime.device)
+                entry.v = torch.zeros((*shape[:3], need.v_head_dim), dtype=runtime.dtype, device=runtime.device)
             if state is not None:
                 entry.state = torch.zeros((max_slots, *state.shape), dtype=state.dtype, device=runtime.device)
             self.entries.append(entry)

@@ -197,3 +197,111 @@ class Qwen3Config(ModelConfig):
         if not out["num_experts"]:
             del out["num_experts"]
         return out
+
+
+@dataclass
+class NiduvikConfig(ModelConfig):
+    """Niduvik: a decoder of layers that each hold one mixer, attention (no rotation; biased, soft-capped, windowed
+    with kept first tokens, a sink in the softmax, blended values, an output gate) or a state-space recurrence, and
+    optionally a clamped gated feed-forward, with an RMS norm before and after each branch.  config.json names the
+    design under `architecture` and lists the layers with their sizes and constants; the keys are read as they
+    stand there:
+
+      vocab, width, norm.eps
+      layers[i].type = "attention": mixer.{heads, kv_heads, dim, vdim, scale, softcap, bias_max, v_mix, mask.{size, keep_first}}
+      layers[i].type = "mamba2":    mixer.{heads, vdim, state, groups, conv, norm_groups}
+      layers[i].mlp = null | {kind: "dense", ff, limit}
+
+    A checkpoint's distance-bias table states its own length; `mixer.bias_rows` gives it for a model that is drawn at
+    random.  The design states no longest context and no end-of-sequence token; `max_position_embeddings` and `eos_token_id`
+    are read if a file has them."""
+
+    width: int = 0
+    norm_eps: float = 0.0
+    layers: list = None
+
+    MODEL_TYPES: ClassVar[tuple[str, ...]] = ("niduvik",)
+    NO_CONTEXT_LIMIT: ClassVar[int] = 1 << 22
+    MIXER_KEYS: ClassVar[dict] = {
+        "attention": {"heads": int, "kv_heads": int, "dim": int, "vdim": int, "scale": float, "softcap": float,
+                      "bias_max": float, "v_mix": bool},
+        "mamba2": {"heads": int, "vdim": int, "state": int, "groups": int, "conv": int, "norm_groups": int},
+    }
+
+    @classmethod
+    def from_dict(cls, raw: dict) -> "NiduvikConfig":
+        norm = raw.get("norm")
+        if not isinstance(norm, dict):
+            raise InvalidRequest("config.json: missing key `norm` (an object with `eps`)")
+        layers = raw.get("layers")
+        if not isinstance(layers, list) or not layers:
+            raise InvalidRequest("config.json: `layers` must be a list of layers")
+        read = []
+        for i, layer in enumerate(layers):
+            if not isinstance(layer, dict):
+                raise InvalidRequest(f"config.json: layers[{i}] must be an object")
+            kind = _require(layer, "type", str, f"mixer of layer {i}")
+            if kind not in cls.MIXER_KEYS:
+                raise InvalidRequest(f"config.json: layers[{i}].type {kind!r}; known: {sorted(cls.MIXER_KEYS)}")
+            mixer = layer.get("mixer")
+            if not isinstance(mixer, dict):
+                raise InvalidRequest(f"config.json: layers[{i}].mixer must be an object")
+            sizes = {key: _require(mixer, key, want, f"layers[{i}].mixer") for key, want in cls.MIXER_KEYS[kind].items()}
+            if kind == "attention":
+                mask = mixer.get("mask")
+                if not isinstance(mask, dict):
+                    raise InvalidRequest(f"config.json: layers[{i}].mixer.mask must be an object")
+                if mixer.get("bias_rows") is not None:          # not a key of the design: the table's rows, for models without a checkpoint
+                    sizes["bias_rows"] = _require(mixer, "bias_rows", int, "rows of the distance-bias table")
+                sizes["mask"] = {"size": _require(mask, "size", int, "window"), "keep_first": _require(mask, "keep_first", int, "kept first tokens")}
+            mlp = layer.get("mlp")
+            if mlp is not None:
+                if not isinstance(mlp, dict):
+                    raise InvalidRequest(f"config.json: layers[{i}].mlp must be null or an object")
+                mlp = {"kind": _require(mlp, "kind", str, "feed-forward kind"), "ff": _require(mlp, "ff", int, "feed-forward width"),
+                       "limit": _require(mlp, "limit", float, "clamp")}
+            read.append({"type": kind, "mixer": sizes, "mlp": mlp})
+        cfg = cls(model_type="niduvik", architectures=["Niduvik"], vocab_size=_require(raw, "vocab", int, "vocabulary"),
+                  max_position_embeddings=int(raw.get("max_position_embeddings") or cls.NO_CONTEXT_LIMIT),
+                  eos_token_id=raw.get("eos_token_id"), width=_require(raw, "width", int, "model width"),
+                  norm_eps=_require(norm, "eps", float, "norm epsilon"), layers=read)
+        cfg.validate()
+        return cfg
+
+    def validate(self) -> None:
+        if self.vocab_size <= 0 or self.width <= 0 or self.max_position_embeddings <= 0:
+            raise InvalidRequest("invalid Niduvik dimensions: every size must be a positive integer")
+        if not math.isfinite(self.norm_eps) or self.norm_eps <= 0:
+            raise InvalidRequest("invalid normalization parameters")
+        for i, layer in enumerate(self.layers):
+            m = layer["mixer"]
+            for key, want in self.MIXER_KEYS[layer["type"]].items():
+                if want is int and m[key] <= 0:
+                    raise InvalidRequest(f"layers[{i}].mixer.{key} must be positive")
+            if layer["type"] == "attention":
+                if m["heads"] % m["kv_heads"]:
+                    raise InvalidRequest(f"layers[{i}]: heads must be a multiple of kv_heads")
+                if m["mask"]["size"] <= 0 or m["mask"]["keep_first"] < 0 or m["softcap"] <= 0 or m["scale"] <= 0:
+                    raise InvalidRequest(f"layers[{i}]: window, kept tokens, soft cap or scale out of range")
+            else:
+                if m["heads"] % m["groups"] or (m["heads"] * m["vdim"]) % m["norm_groups"]:
+                    raise InvalidRequest(f"layers[{i}]: heads must be a multiple of groups, heads * vdim of norm_groups")
+            mlp = layer["mlp"]
+            if mlp is not None and (mlp["kind"] != "dense" or mlp["ff"] <= 0 or mlp["limit"] <= 0):
+                raise InvalidRequest(f"layers[{i}].mlp: only kind `dense` with positive `ff` and `limit` is built")
+        if self.eos_token_id is not None:
+            self.eos_ids()
+
+    def eos_ids(self, folder: str | None = None) -> list[int]:
+        if self.eos_token_id is None and (folder is None or not os.path.exists(os.path.join(folder, "generation_config.json"))):
+            return []                # the design names no end-of-sequence token: generation ends by length
+        return super().eos_ids(folder)
+
+    def to_dict(self) -> dict:
+        out = {"architecture": "Niduvik", "vocab": self.vocab_size, "width": self.width, "norm": {"eps": self.norm_eps},
+               "layers": self.layers}
+        if self.max_position_embeddings != self.NO_CONTEXT_LIMIT:
+            out["max_position_embeddings"] = self.max_position_embeddings
+        if self.eos_token_id is not None:
+            out["eos_token_id"] = self.eos_token_id
+        return out

@@ -183,6 +183,22 @@ def kernel_library() -> ctypes.CDLL:
     return _load("kernels", builder)
 
 
+HYBRID_KERNEL_SOURCES = ("hybrid_elementwise.cu", "attention_biased.cu", "ssm_scan.cu")
+
+
+def hybrid_kernel_library() -> ctypes.CDLL:
+    """The kernels of layers with biased, windowed attention and of state-space recurrences (every size at run
+    time); compiled when a model first needs one of them."""
+    folder = os.path.join(CSRC, "kernels")
+
+    def builder():
+        sources = [os.path.join(folder, f) for f in HYBRID_KERNEL_SOURCES]
+        nvcc = _find("nvcc", ("/usr/local/cuda/bin/nvcc",))
+        return _build("mrs_hybrid", sources, [nvcc], NVCC_FLAGS, [], folder)
+
+    return _load("hybrid", builder)
+
+
 def specialised_kernel_library(source: str, defines: dict[str, int], extra_flags: tuple[str, ...] = ()) -> ctypes.CDLL:
     """One kernel source compiled for fixed sizes, e.g. attention for one head size."""
     folder = os.path.join(CSRC, "kernels")
@@ -206,4 +222,5 @@ SPECIALISED_BUILDS = tuple((lambda d=d: specialised_kernel_library("attention_mm
                            for d in PREBUILT_HEAD_DIMS) + \
     tuple((lambda d=d: specialised_kernel_library("attention_decode_tma.cu", {"MRS_HEAD_DIM": d})) for d in (64, 128)) + \
     tuple((lambda d=d: specialised_kernel_library("attention_prefill_tc.cu", {"MRS_HEAD_DIM": d})) for d in (64, 128)) + \
-    (lambda: specialised_kernel_library("gemm_tc.cu", {}), lambda: specialised_kernel_library("gemm_many_rows.cu", {}))
+    (lambda: specialised_kernel_library("gemm_tc.cu", {}), lambda: specialised_kernel_library("gemm_many_rows.cu", {}),
+     hybrid_kernel_library)

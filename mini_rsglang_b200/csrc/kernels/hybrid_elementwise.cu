@@ -1,0 +1,176 @@
+// Row-wise kernels of layers that norm a branch before it joins the stream, clamp a gated
+// feed-forward, add biases to q/k/v and blend values between layers, and norm a gated
+// recurrence output in parts.  All statistics, sums and gates are float32; T is the engine's
+// dtype (float or bfloat16) and is only what a kernel hands to the next product or the cache.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------------------
+// stream += rmsnorm(branch) * w_post;  out = rmsnorm(stream) * w_next   (w_next may be null: sum only)
+// branch float32 [rows, width] (a product's float32 sums), stream float32, out T.
+// One block a row; the row is read three times from L1/L2.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void postnorm_add_norm_kernel(float* __restrict__ stream, const float* __restrict__ branch,
+                                         const float* __restrict__ w_post, const float* __restrict__ w_next, float eps_post,
+                                         float eps_next, T* __restrict__ out, int width) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[33];
+    const size_t r = blockIdx.x;
+    float* res = stream + r * width;
+    const float* a = branch + r * width;
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) sum += a[i] * a[i];
+    const float scale_a = 1.0f / sqrtf(block_sum(sum, scratch) / (float)width + eps_post);
+    sum = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = res[i] + a[i] * scale_a * w_post[i];
+        res[i] = v;
+        sum += v * v;
+    }
+    if (w_next == nullptr) return;
+    const float scale_v = 1.0f / sqrtf(block_sum(sum, scratch) / (float)width + eps_next);
+    T* o = out + r * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_float<T>(res[i] * scale_v * w_next[i]);
+}
+
+MRS_EXPORT int mrs_postnorm_add_norm(int is_bf16, float* stream, const float* branch, const float* w_post, const float* w_next,
+                                     float eps_post, float eps_next, void* out, int rows, int width, void* s) {
+    if (rows <= 0) return 0;
+    if (width <= 0) return MRS_BAD_ARGUMENT;
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    if (is_bf16)
+        MRS_LAUNCH(postnorm_add_norm_kernel<bf16>, rows, threads, 0, s, stream, branch, w_post, w_next, eps_post, eps_next, (bf16*)out, width);
+    else
+        MRS_LAUNCH(postnorm_add_norm_kernel<float>, rows, threads, 0, s, stream, branch, w_post, w_next, eps_post, eps_next, (float*)out, width);
+    MRS_RETURN_LAUNCH_STATUS();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Clamped gated unit: g = min(gate, limit), u = clamp(up, -limit, limit); out = g * sigmoid(alpha g) * (u + 1).
+// gate_up [tokens, 2 * inter]: all gate columns, then all up columns.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void glu_clamped_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long total, int inter, float limit,
+                                   float alpha) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / inter;
+        const int c = (int)(i - t * inter);
+        const float g = fminf(to_float(gate_up[t * 2 * inter + c]), limit);
+        const float u = fminf(fmaxf(to_float(gate_up[t * 2 * inter + inter + c]), -limit), limit);
+        out[i] = from_float<T>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+    }
+}
+
+MRS_EXPORT int mrs_glu_clamped(int is_bf16, const void* gate_up, void* out, int tokens, int inter, float limit, float alpha, void* s) {
+    const long long total = (long long)tokens * inter;
+    if (total <= 0) return 0;
+    long long blocks = (total + 255) / 256;
+    const long long cap = (long long)mrs_sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    if (is_bf16)
+        MRS_LAUNCH(glu_clamped_kernel<bf16>, (unsigned)blocks, 256, 0, s, (const bf16*)gate_up, (bf16*)out, total, inter, limit, alpha);
+    else
+        MRS_LAUNCH(glu_clamped_kernel<float>, (unsigned)blocks, 256, 0, s, (const float*)gate_up, (float*)out, total, inter, limit, alpha);
+    MRS_RETURN_LAUNCH_STATUS();
+}
+
+// ---------------------------------------------------------------------------------------------
+// After the fused q|k|v|gate projection (float32 sums [tokens, nq*d + nkv*d + nkv*e + nq]):
+// adds the biases of q, k and v; q -> q_out (T); k -> key pages; v, blended with the values that an
+// earlier layer left for the same token (v <- (1 - lambda) v + lambda v_first), -> value pages;
+// sigmoid of the gate columns -> gate_out float32 [tokens, nq].
+// mix_mode 0: no blending; 1: this layer's own values (with bias) are written to v_first; 2: blend from v_first.
+// Key pages [pages, nkv, page, d], value pages [pages, nkv, page, e]; slot < 0 writes nothing.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void qkv_bias_store_kernel(const float* __restrict__ proj, const float* __restrict__ bias, T* __restrict__ q_out,
+                                      T* __restrict__ k_cache, T* __restrict__ v_cache, const int* __restrict__ slots,
+                                      float* __restrict__ v_first, float* __restrict__ gate_out, int nq, int nkv, int d, int e,
+                                      int page_size, int mix_mode, float lambda, int has_gate) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t t = blockIdx.x;
+    const int qw = nq * d, kw = nkv * d, vw = nkv * e;
+    const int total = qw + kw + vw + (has_gate ? nq : 0);
+    const float* row = proj + t * total;
+    const int slot = slots ? slots[t] : -1;
+    const int page = slot >= 0 ? slot / page_size : 0, in_page = slot >= 0 ? slot % page_size : 0;
+    for (int c = threadIdx.x; c < total; c += blockDim.x) {
+        if (c < qw) {
+            q_out[t * qw + c] = from_float<T>(row[c] + (bias ? bias[c] : 0.0f));
+        } else if (c < qw + kw) {
+            const int j = c - qw, head = j / d, x = j % d;
+            if (slot >= 0 && k_cache)
+                k_cache[(((size_t)page * nkv + head) * page_size + in_page) * d + x] = from_float<T>(row[c] + (bias ? bias[c] : 0.0f));
+        } else if (c < qw + kw + vw) {
+            const int j = c - qw - kw, head = j / e, x = j % e;
+            float v = row[c] + (bias ? bias[c] : 0.0f);
+            if (mix_mode == 1) v_first[t * vw + j] = v;
+            else if (mix_mode == 2) v = (1.0f - lambda) * v + lambda * v_first[t * vw + j];
+            if (slot >= 0 && v_cache)
+                v_cache[(((size_t)page * nkv + head) * page_size + in_page) * e + x] = from_float<T>(v);
+        } else {
+            const int h = c - qw - kw - vw;
+            gate_out[t * nq + h] = 1.0f / (1.0f + expf(-row[c]));
+        }
+    }
+}
+
+MRS_EXPORT int mrs_qkv_bias_store(int is_bf16, const float* proj, const float* bias, void* q_out, void* k_cache, void* v_cache,
+                                  const int* slots, float* v_first, float* gate_out, int tokens, int nq, int nkv, int d, int e,
+                                  int page_size, int mix_mode, float lambda, int has_gate, void* s) {
+    if (tokens <= 0) return 0;
+    if (nq <= 0 || nkv <= 0 || d <= 0 || e <= 0 || page_size <= 0 || (mix_mode && !v_first) || (has_gate && !gate_out))
+        return MRS_BAD_ARGUMENT;
+    if (is_bf16)
+        MRS_LAUNCH(qkv_bias_store_kernel<bf16>, tokens, 256, 0, s, proj, bias, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, slots,
+                   v_first, gate_out, nq, nkv, d, e, page_size, mix_mode, lambda, has_gate);
+    else
+        MRS_LAUNCH(qkv_bias_store_kernel<float>, tokens, 256, 0, s, proj, bias, (float*)q_out, (float*)k_cache, (float*)v_cache, slots,
+                   v_first, gate_out, nq, nkv, d, e, page_size, mix_mode, lambda, has_gate);
+    MRS_RETURN_LAUNCH_STATUS();
+}
+
+// ---------------------------------------------------------------------------------------------
+// out = rmsnorm_in_parts(y * silu(z)) * weight: the row of `inner` elements is cut into `parts` equal parts,
+// each divided by its own root mean square.  y float32 [tokens, inner]; z float32, a column range of a wider
+// row (z_stride elements a row); out T [tokens, inner].  One block a (token, part).
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void gated_part_norm_kernel(const float* __restrict__ y, const float* __restrict__ z, int z_stride,
+                                       const float* __restrict__ weight, float eps, T* __restrict__ out, int inner, int parts) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[33];
+    const size_t t = blockIdx.x;
+    const int part = blockIdx.y, width = inner / parts, first = part * width;
+    const float* yr = y + t * inner + first;
+    const float* zr = z + t * z_stride + first;
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float g = yr[i] * (zr[i] / (1.0f + expf(-zr[i])));
+        sum += g * g;
+    }
+    const float scale = 1.0f / sqrtf(block_sum(sum, scratch) / (float)width + eps);
+    T* o = out + t * inner + first;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float g = yr[i] * (zr[i] / (1.0f + expf(-zr[i])));
+        o[i] = from_float<T>(g * scale * weight[first + i]);
+    }
+}
+
+MRS_EXPORT int mrs_gated_part_norm(int is_bf16, const float* y, const float* z, int z_stride, const float* weight, float eps,
+                                   void* out, int tokens, int inner, int parts, void* s) {
+    if (tokens <= 0) return 0;
+    if (parts <= 0 || inner <= 0 || inner % parts) return MRS_BAD_ARGUMENT;
+    const int width = inner / parts;
+    const int threads = width >= 1024 ? 256 : (width >= 256 ? 128 : 64);
+    if (is_bf16)
+        MRS_LAUNCH(gated_part_norm_kernel<bf16>, dim3(tokens, parts), threads, 0, s, y, z, z_stride, weight, eps, (bf16*)out, inner, parts);
+    else
+        MRS_LAUNCH(gated_part_norm_kernel<float>, dim3(tokens, parts), threads, 0, s, y, z, z_stride, weight, eps, (float*)out, inner, parts);
+    MRS_RETURN_LAUNCH_STATUS();
+}

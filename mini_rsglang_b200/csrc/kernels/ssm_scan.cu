@@ -1,0 +1,182 @@
+// A selective state-space recurrence with a short causal convolution in front of it (the "state-space
+// duality" layer): per head h (with its group g of B and C)
+//     dt_t = softplus(raw_t + dt_bias_h);   S_t = exp(-exp(A_log_h) dt_t) S_(t-1) + dt_t B_t x_t^T;   y_t = S_t^T C_t + D_h x_t
+// with S [N, P] float32 per (request, head), kept in the request's state slot between steps, and in front of
+// it, per channel c of (x | B | C):  u_t = silu(bias_c + sum_k w[c, k] in_(t - (taps - 1 - k))), zeros before the
+// sequence's start; the last taps - 1 inputs of a request are part of its state too.
+//
+// Everything here is float32.  A request's rows are contiguous in a step; where a sequence starts at position 0
+// its state counts as zero, whatever the slot held (slots are used again).  State slot -1: a padding sequence,
+// nothing is read or written.  The step's facts come from device arrays only, so a step can be recorded.
+#include "common.cuh"
+
+#define SSM_MAX_TAPS 16
+#define SSM_PER_LANE 16         // state rows (of N) a thread keeps in registers
+
+// in [tokens, in_stride] float32, the channels at column `offset`; conv_state [slots, (taps - 1), channels] with
+// `state_stride` floats from slot to slot; out [tokens, channels].
+__global__ void causal_conv_silu_kernel(const float* __restrict__ in, int in_stride, int offset, const float* __restrict__ weight,
+                                        const float* __restrict__ bias, const float* __restrict__ conv_state, long long state_stride,
+                                        const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                        const int* __restrict__ q_start, const int* __restrict__ state_slots,
+                                        float* __restrict__ out, int channels, int taps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int seq = seq_of_token[t];
+    const int start_row = q_start[seq], end_row = q_start[seq + 1];
+    const int slot = state_slots[seq];
+    const int pos = positions[t];
+    const bool real = t >= start_row && t < end_row && slot >= 0;
+    const float* state = conv_state + (real ? (long long)slot * state_stride : 0);
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
+        float acc = 0.0f;
+        if (real) {
+            acc = bias ? bias[c] : 0.0f;
+            for (int k = 0; k < taps; ++k) {
+                const int back = taps - 1 - k;
+                if (pos - back < 0) continue;                       // before the sequence's start
+                const int row = t - back;
+                float x;
+                if (row >= start_row) x = in[(size_t)row * in_stride + offset + c];
+                else x = state[(size_t)(taps - 1 - (start_row - row)) * channels + c];     // the inputs of earlier steps
+                acc += weight[(size_t)c * taps + k] * x;
+            }
+            acc = acc / (1.0f + expf(-acc));
+        }
+        out[(size_t)t * channels + c] = acc;
+    }
+}
+
+// After the convolution has read the old state: the last taps - 1 inputs of every sequence become its state.
+__global__ void conv_state_update_kernel(const float* __restrict__ in, int in_stride, int offset, float* __restrict__ conv_state,
+                                         long long state_stride, const int* __restrict__ positions, const int* __restrict__ q_start,
+                                         const int* __restrict__ state_slots, int channels, int taps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int seq = blockIdx.x;
+    const int start_row = q_start[seq], n = q_start[seq + 1] - start_row;
+    const int slot = state_slots[seq];
+    if (slot < 0 || n <= 0) return;
+    const int start_pos = positions[start_row];
+    float* state = conv_state + (long long)slot * state_stride;
+    const int keep = taps - 1;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
+        float next[SSM_MAX_TAPS];
+#pragma unroll
+        for (int j = 0; j < SSM_MAX_TAPS; ++j) {
+            if (j >= keep) break;
+            const int rel = n - keep + j;                 // row of the portion that lands in place j
+            if (rel >= 0) next[j] = in[(size_t)(start_row + rel) * in_stride + offset + c];
+            else next[j] = start_pos + rel >= 0 ? state[(size_t)(j + n) * channels + c] : 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < SSM_MAX_TAPS; ++j) {
+            if (j >= keep) break;
+            state[(size_t)j * channels + c] = next[j];
+        }
+    }
+}
+
+MRS_EXPORT int mrs_causal_conv_silu(const float* in, int in_stride, int offset, const float* weight, const float* bias,
+                                    float* conv_state, long long state_stride, const int* positions, const int* seq_of_token,
+                                    const int* q_start, const int* state_slots, float* out, int tokens, int sequences, int channels,
+                                    int taps, int update_state, void* stream) {
+    if (tokens <= 0) return 0;
+    if (channels <= 0 || taps <= 0 || taps > SSM_MAX_TAPS) return MRS_BAD_ARGUMENT;
+    const int threads = 128;
+    int per_row = (channels + threads - 1) / threads;
+    if (per_row > 64) per_row = 64;
+    MRS_LAUNCH(causal_conv_silu_kernel, dim3(tokens, per_row), threads, 0, stream, in, in_stride, offset, weight, bias,
+               (const float*)conv_state, state_stride, positions, seq_of_token, q_start, state_slots, out, channels, taps);
+    if (update_state && taps > 1)
+        MRS_LAUNCH(conv_state_update_kernel, dim3(sequences, per_row), threads, 0, stream, in, in_stride, offset, conv_state,
+                   state_stride, positions, q_start, state_slots, channels, taps);
+    MRS_RETURN_LAUNCH_STATUS();
+}
+
+// ---------------------------------------------------------------------------------------------
+// The recurrence, token by token.  One block per (sequence, head); thread (p, s): column p of S and the rows
+// n = s * per + i of it in registers (lanes of one p are neighbours, so that y's sum over n is a few shuffles).
+// xbc [tokens, heads * P + 2 * groups * N] float32 (x | B | C after convolution and silu), raw dt a column range of
+// the projection's rows, y [tokens, heads * P] float32.  ssm_state [slots, heads, N, P].
+// The loads of the next token are issued before the arithmetic of this one.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.0f) + log1pf(expf(-fabsf(x))); }
+
+__global__ void ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt_in, int dt_stride,
+                                const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
+                                float* __restrict__ ssm_state, long long state_stride, const int* __restrict__ positions,
+                                const int* __restrict__ q_start, const int* __restrict__ state_slots, float* __restrict__ y,
+                                int heads, int groups, int N, int P, int lanes_per_column, int per, int write_state) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int seq = blockIdx.x, head = blockIdx.y;
+    const int start_row = q_start[seq], end_row = q_start[seq + 1];
+    const int slot = state_slots[seq];
+    if (slot < 0 || end_row <= start_row) return;
+    const int s = threadIdx.x % lanes_per_column, p = threadIdx.x / lanes_per_column;
+    const bool live = p < P;
+    const int group = head / (heads / groups);
+    const int inner = heads * P, row_width = inner + 2 * groups * N;
+    const int n0 = s * per;
+    float* state = ssm_state + (long long)slot * state_stride + (size_t)head * N * P;
+    float S[SSM_PER_LANE];
+    const bool fresh = positions[start_row] == 0;
+#pragma unroll
+    for (int i = 0; i < SSM_PER_LANE; ++i)
+        S[i] = (!fresh && live && i < per && n0 + i < N) ? state[(size_t)(n0 + i) * P + p] : 0.0f;
+    const float bias = dt_bias[head], rate = -expf(a_log[head]), skip = d_skip[head];
+
+    float b_next[SSM_PER_LANE], c_next[SSM_PER_LANE], x_next = 0.0f, dt_next = 0.0f;
+    auto load = [&](int row) {
+        const float* r = xbc + (size_t)row * row_width;
+        x_next = live ? r[head * P + p] : 0.0f;
+        dt_next = dt_in[(size_t)row * dt_stride + head];
+#pragma unroll
+        for (int i = 0; i < SSM_PER_LANE; ++i) {
+            const bool in = i < per && n0 + i < N;
+            b_next[i] = in ? r[inner + group * N + n0 + i] : 0.0f;
+            c_next[i] = in ? r[inner + groups * N + group * N + n0 + i] : 0.0f;
+        }
+    };
+    load(start_row);
+    for (int row = start_row; row < end_row; ++row) {
+        float b[SSM_PER_LANE], c[SSM_PER_LANE];
+        const float x = x_next, dt = softplus_f(dt_next + bias);
+#pragma unroll
+        for (int i = 0; i < SSM_PER_LANE; ++i) b[i] = b_next[i], c[i] = c_next[i];
+        if (row + 1 < end_row) load(row + 1);
+        const float decay = expf(rate * dt), dx = dt * x;
+        float sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < SSM_PER_LANE; ++i) {
+            S[i] = decay * S[i] + dx * b[i];
+            sum += S[i] * c[i];
+        }
+        for (int o = 1; o < lanes_per_column; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (live && s == 0) y[(size_t)row * inner + head * P + p] = sum + skip * x;
+    }
+    if (write_state && live) {
+#pragma unroll
+        for (int i = 0; i < SSM_PER_LANE; ++i)
+            if (i < per && n0 + i < N) state[(size_t)(n0 + i) * P + p] = S[i];
+    }
+}
+
+MRS_EXPORT int mrs_ssm_scan(const float* xbc, const float* dt_in, int dt_stride, const float* dt_bias, const float* a_log,
+                            const float* d_skip, float* ssm_state, long long state_stride, const int* positions, const int* q_start,
+                            const int* state_slots, float* y, int sequences, int heads, int groups, int N, int P, int write_state,
+                            void* stream) {
+    if (sequences <= 0) return 0;
+    if (heads <= 0 || groups <= 0 || heads % groups || N <= 0 || P <= 0) return MRS_BAD_ARGUMENT;
+    int lanes = 1;
+    while (lanes < 32 && (N + lanes - 1) / lanes > SSM_PER_LANE) lanes <<= 1;
+    const int per = (N + lanes - 1) / lanes;
+    if (per > SSM_PER_LANE) return MRS_BAD_ARGUMENT;                 // N above 512
+    const int threads = (P * lanes + 31) / 32 * 32;
+    if (threads > 1024) return MRS_BAD_ARGUMENT;
+    MRS_LAUNCH(ssm_scan_kernel, dim3(sequences, heads), threads, 0, stream, xbc, dt_in, dt_stride, dt_bias, a_log, d_skip, ssm_state,
+               state_stride, positions, q_start, state_slots, y, heads, groups, N, P, lanes, per, write_state);
+    MRS_RETURN_LAUNCH_STATUS();
+}

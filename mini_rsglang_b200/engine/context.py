@@ -41,6 +41,9 @@ class StepContext:
     # model calls observe(label, tensor [T, width]) with what the reference's observer sees under the same
     # labels, and the parts take the kernels that leave those tensors (no product with a fused epilogue).
     observe: object = None
+    # A run whose results nobody keeps (the trial run before a step is recorded): the layers write neither keys and
+    # values nor state, so that the recorded step, which runs next, finds the cache as the step before left it.
+    rehearsal: bool = False
     label: str = ""                    # the running layer's label ("layer3"), set by the model while observing
     # what the parts of one step share (the rotations' cosines and sines); the model empties it when a step begins
     shared: dict = field(default_factory=dict)

@@ -31,7 +31,7 @@ from ..errors import EngineError, InvalidRequest
 from ..models.registry import load_config
 from .runner import ModelRunner, SequenceStep
 
-MAX_LIVE = 8      # state slots; a trace holds up to four live requests
+MAX_LIVE = 4      # state slots: a trace holds up to four live requests, so slots are used again
 
 
 class Replayer:

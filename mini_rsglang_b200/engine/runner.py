@@ -356,13 +356,16 @@ class ModelRunner:
 
     def _record(self, record: _Recorded, ctx: StepContext) -> None:
         """Runs the context's step once outside a recording (first use of every kernel, scratch buffers at
-        their sizes), then records it."""
+        their sizes), then records it.  The trial run writes nothing into the cache: a layer that keeps a state
+        would otherwise advance it twice."""
         record.ctx = ctx
         stream = torch.cuda.current_stream()
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(stream)
+        ctx.rehearsal = True
         with torch.no_grad(), torch.cuda.stream(side):
             self.model.forward(ctx, self.storage)
+        ctx.rehearsal = False
         stream.wait_stream(side)
         graph = torch.cuda.CUDAGraph()
         counted = kernels.launch_count

@@ -1011,3 +1011,189 @@ def check_device_errors(certain: bool = False) -> None:
         for counters in list(_counters.values()) + [state["counters"] for state in _gemm_state.values()]:
             counters.zero_()
         raise BackendError("; ".join(failed) + "; the step's result is invalid")
+
+
+# ------------------------------------------------------------------------------------------------
+# layers with a norm after each branch, biased and windowed attention, state-space recurrences
+# ------------------------------------------------------------------------------------------------
+_c_ll = ctypes.c_longlong
+_HYBRID_SIGNATURES = {
+    "mrs_postnorm_add_norm": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_float, _c_float, _c_vp, _c_int, _c_int, _c_vp],
+    "mrs_glu_clamped": [_c_int, _c_vp, _c_vp, _c_int, _c_int, _c_float, _c_float, _c_vp],
+    "mrs_qkv_bias_store": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_int,
+                           _c_int, _c_int, _c_float, _c_int, _c_vp],
+    "mrs_gated_part_norm": [_c_int, _c_vp, _c_vp, _c_int, _c_vp, _c_float, _c_vp, _c_int, _c_int, _c_int, _c_vp],
+    "mrs_attention_biased_simt": [_c_int] + [_c_vp] * 9 + [_c_int] * 7 + [_c_float, _c_float, _c_int, _c_int, _c_int, _c_int, _c_vp],
+    "mrs_causal_conv_silu": [_c_vp, _c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_ll, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int,
+                             _c_int, _c_int, _c_int, _c_vp],
+    "mrs_ssm_scan": [_c_vp, _c_vp, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_ll, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int,
+                     _c_int, _c_int, _c_int, _c_vp],
+}
+_hybrid_lib = None
+
+
+def hybrid_library() -> ctypes.CDLL:
+    global _hybrid_lib
+    if _hybrid_lib is None:
+        if not torch.cuda.is_available():
+            raise BackendError("no CUDA device: the engine has no CPU path")
+        from .csrc.build import hybrid_kernel_library
+
+        lib = hybrid_kernel_library()
+        for name, argtypes in _HYBRID_SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = argtypes
+            fn.restype = _c_int
+        _hybrid_lib = lib
+    return _hybrid_lib
+
+
+def postnorm_add_norm(stream: torch.Tensor, branch: torch.Tensor, post_weight: torch.Tensor, post_eps: float,
+                      next_weight: torch.Tensor | None, next_eps: float, out: torch.Tensor | None) -> None:
+    """stream += rmsnorm(branch) * post_weight; with `next_weight`, out = rmsnorm(stream) * next_weight.
+    `branch` holds a product's float32 sums; the norms and the sum are float32."""
+    rows, width = stream.shape
+    _need(stream, torch.float32, "postnorm stream")
+    _need(branch, torch.float32, "postnorm branch", (rows, width))
+    _need(post_weight, torch.float32, "postnorm weight", (width,))
+    if next_weight is not None:
+        _need(next_weight, torch.float32, "next norm weight", (width,))
+        _need(out, None, "postnorm out", (rows, width))
+    _check(hybrid_library().mrs_postnorm_add_norm(_is_bf16(out.dtype) if out is not None else 0, stream.data_ptr(),
+                                                  branch.data_ptr(), post_weight.data_ptr(), _ptr(next_weight), float(post_eps),
+                                                  float(next_eps), _ptr(out), rows, width, _stream()), "postnorm_add_norm")
+
+
+def glu_clamped(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> None:
+    """out = g * sigmoid(alpha * g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit); `gate_up` holds
+    all gate columns and then all up columns."""
+    tokens, inter = out.shape
+    _need(gate_up, out.dtype, "gate_up", (tokens, 2 * inter))
+    _need(out, None, "glu_clamped out")
+    _check(hybrid_library().mrs_glu_clamped(_is_bf16(out.dtype), gate_up.data_ptr(), out.data_ptr(), tokens, inter, float(limit),
+                                            float(alpha), _stream()), "glu_clamped")
+
+
+def qkv_bias_store(proj: torch.Tensor, bias: torch.Tensor | None, q_out: torch.Tensor, k_cache: torch.Tensor | None,
+                   v_cache: torch.Tensor | None, slots: torch.Tensor | None, nq: int, nkv: int, d: int, e: int,
+                   v_first: torch.Tensor | None = None, mix_mode: int = 0, mix: float = 0.0,
+                   gate_out: torch.Tensor | None = None) -> None:
+    """After the fused projection q | k | v (| one gate column a query head), float32: biases added, q to `q_out`, k into
+    the key pages [pages, nkv, page, d], v into the value pages [pages, nkv, page, e] at `slots`, sigmoid(gate) to
+    `gate_out` [tokens, nq] float32.  `mix_mode` 1 leaves this layer's values in `v_first` [tokens, nkv * e] float32;
+    2 stores (1 - mix) v + mix v_first instead of v."""
+    tokens = proj.shape[0]
+    width = nq * d + nkv * d + nkv * e
+    _need(proj, torch.float32, "qkv projection", (tokens, width + (nq if gate_out is not None else 0)))
+    if bias is not None:
+        _need(bias, torch.float32, "qkv bias", (width,))
+    _need(q_out, None, "q_out", (tokens, nq * d))
+    page_size = 1
+    if k_cache is not None:
+        page_size = k_cache.shape[2]
+        _need(k_cache, q_out.dtype, "key pages")
+        _need(v_cache, q_out.dtype, "value pages")
+        if tuple(k_cache.shape[1:]) != (nkv, page_size, d) or tuple(v_cache.shape[1:]) != (nkv, page_size, e):
+            raise InvalidRequest("qkv_bias_store: the pages do not match heads, page size and head sizes")
+        _need(slots, torch.int32, "slots", (tokens,))
+    if mix_mode:
+        _need(v_first, torch.float32, "v_first", (tokens, nkv * e))
+    if gate_out is not None:
+        _need(gate_out, torch.float32, "gate", (tokens, nq))
+    _check(hybrid_library().mrs_qkv_bias_store(_is_bf16(q_out.dtype), proj.data_ptr(), _ptr(bias), q_out.data_ptr(), _ptr(k_cache),
+                                               _ptr(v_cache), _ptr(slots) if k_cache is not None else None, _ptr(v_first),
+                                               _ptr(gate_out), tokens, nq, nkv, d, e, page_size, int(mix_mode), float(mix),
+                                               int(gate_out is not None), _stream()), "qkv_bias_store")
+
+
+def gated_part_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, parts: int) -> None:
+    """out = (y * silu(z)), each of `parts` equal parts of a row divided by its own root mean square, times weight.
+    `z` may be a column range of wider float32 rows."""
+    tokens, inner = y.shape
+    _need(y, torch.float32, "recurrence output")
+    if not z.is_cuda or z.dtype != torch.float32 or tuple(z.shape) != (tokens, inner) or z.stride(1) != 1:
+        raise InvalidRequest("gated_part_norm: the gate must be float32 [tokens, inner] with unit column stride")
+    _need(weight, torch.float32, "part norm weight", (inner,))
+    _need(out, None, "part norm out", (tokens, inner))
+    if inner % parts:
+        raise InvalidRequest("gated_part_norm: the row is no multiple of the parts")
+    _check(hybrid_library().mrs_gated_part_norm(_is_bf16(out.dtype), y.data_ptr(), z.data_ptr(), z.stride(0), weight.data_ptr(),
+                                                float(eps), out.data_ptr(), tokens, inner, int(parts), _stream()), "gated_part_norm")
+
+
+def attention_biased_simt(q, k_cache, v_cache, positions, seq_of_token, block_table, out, nq: int, nkv: int, d: int, e: int,
+                          scale: float, cap: float = 0.0, window: int = 0, keep_first: int = 0, bias: torch.Tensor | None = None,
+                          gate: torch.Tensor | None = None, sink: bool = False) -> None:
+    """Causal paged attention with a soft cap on the scores, a bias by distance (`bias` float32 [rows, nq], the last row
+    for every larger distance), a window that keeps the first `keep_first` positions, an optional sink in the softmax
+    and an optional gate a (token, head); keys of d and values of e elements.  One warp per (token, head)."""
+    tokens = q.shape[0]
+    _need(q, None, "q", (tokens, nq * d))
+    _need(k_cache, q.dtype, "key pages")
+    _need(v_cache, q.dtype, "value pages")
+    _need(out, q.dtype, "attention out", (tokens, nq * e))
+    _need(positions, torch.int32, "positions", (tokens,))
+    _need(seq_of_token, torch.int32, "seq_of_token", (tokens,))
+    _need(block_table, torch.int32, "block_table")
+    page_size = k_cache.shape[2]
+    if tuple(k_cache.shape[1:]) != (nkv, page_size, d) or tuple(v_cache.shape[1:]) != (nkv, page_size, e):
+        raise InvalidRequest("attention: the pages do not match heads and head sizes")
+    if bias is not None:
+        _need(bias, torch.float32, "distance bias")
+        if bias.dim() != 2 or bias.shape[1] != nq:
+            raise InvalidRequest("attention: the distance bias must be [rows, query heads]")
+    if gate is not None:
+        _need(gate, torch.float32, "attention gate", (tokens, nq))
+    _check(hybrid_library().mrs_attention_biased_simt(
+        _is_bf16(q.dtype), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), positions.data_ptr(), seq_of_token.data_ptr(),
+        block_table.data_ptr(), _ptr(bias), _ptr(gate), out.data_ptr(), tokens, nq, nkv, d, e, page_size, block_table.shape[1],
+        float(scale), float(cap), int(window), int(keep_first), bias.shape[0] if bias is not None else 0, int(sink), _stream()),
+        "attention_biased_simt")
+
+
+def causal_conv_silu(proj: torch.Tensor, offset: int, weight: torch.Tensor, bias: torch.Tensor | None, conv_state: torch.Tensor,
+                     positions, seq_of_token, q_start, state_slots, out: torch.Tensor, update_state: bool = True) -> None:
+    """out[t, c] = silu(bias[c] + sum_k weight[c, k] * in[t - (taps - 1 - k), c]) over the columns offset .. offset + channels
+    of the float32 rows `proj`, zeros before a sequence's start, inputs of earlier steps from `conv_state`
+    [slots, taps - 1, channels] (a view: rows of a wider per-slot state); afterwards the state holds the last taps - 1 inputs."""
+    tokens = proj.shape[0]
+    channels, taps = weight.shape
+    _need(proj, torch.float32, "conv input")
+    _need(weight, torch.float32, "conv weight")
+    _need(out, torch.float32, "conv out", (tokens, channels))
+    if bias is not None:
+        _need(bias, torch.float32, "conv bias", (channels,))
+    if conv_state.dtype != torch.float32 or conv_state.dim() != 3 or tuple(conv_state.shape[1:]) != (max(taps - 1, 0), channels) or \
+            (taps > 1 and (conv_state.stride(2) != 1 or conv_state.stride(1) != channels)):
+        raise InvalidRequest("causal_conv_silu: the state must be float32 [slots, taps - 1, channels], dense within a slot")
+    if offset < 0 or offset + channels > proj.shape[1]:
+        raise InvalidRequest("causal_conv_silu: the channels lie outside the rows")
+    sequences = state_slots.shape[0]
+    _check(hybrid_library().mrs_causal_conv_silu(proj.data_ptr(), proj.shape[1], int(offset), weight.data_ptr(), _ptr(bias),
+                                                 conv_state.data_ptr(), conv_state.stride(0), positions.data_ptr(),
+                                                 seq_of_token.data_ptr(), q_start.data_ptr(), state_slots.data_ptr(), out.data_ptr(),
+                                                 tokens, sequences, channels, taps, int(update_state), _stream()), "causal_conv_silu")
+
+
+def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dt_bias, a_log, d_skip, ssm_state: torch.Tensor, positions, q_start, state_slots,
+             y: torch.Tensor, heads: int, groups: int, n_state: int, head_dim: int, write_state: bool = True) -> None:
+    """The recurrence S_t = exp(-exp(A_log) dt_t) S_(t-1) + dt_t B_t x_t^T, y_t = S_t^T C_t + D x_t with dt_t =
+    softplus(raw + dt_bias), per (sequence, head), token by token in float32.  `xbc` [tokens, heads * P + 2 * groups * N]
+    float32 holds x | B | C; `dt` the raw step sizes (a column range of wider float32 rows); `ssm_state`
+    [slots, heads, N, P] float32 (a view: dense within a slot); a sequence that starts at position 0 starts from zero."""
+    tokens = xbc.shape[0]
+    inner = heads * head_dim
+    _need(xbc, torch.float32, "x|B|C", (tokens, inner + 2 * groups * n_state))
+    if dt.dtype != torch.float32 or tuple(dt.shape) != (tokens, heads) or dt.stride(1) != 1:
+        raise InvalidRequest("ssm_scan: dt must be float32 [tokens, heads] with unit column stride")
+    for t, name in ((dt_bias, "dt_bias"), (a_log, "A_log"), (d_skip, "D")):
+        _need(t, torch.float32, name, (heads,))
+    if ssm_state.dtype != torch.float32 or tuple(ssm_state.shape[1:]) != (heads, n_state, head_dim) or \
+            ssm_state.stride(3) != 1 or ssm_state.stride(2) != head_dim or ssm_state.stride(1) != n_state * head_dim:
+        raise InvalidRequest("ssm_scan: the state must be float32 [slots, heads, N, P], dense within a slot")
+    _need(y, torch.float32, "recurrence output", (tokens, inner))
+    sequences = state_slots.shape[0]
+    _check(hybrid_library().mrs_ssm_scan(xbc.data_ptr(), dt.data_ptr(), dt.stride(0), dt_bias.data_ptr(), a_log.data_ptr(),
+                                         d_skip.data_ptr(), ssm_state.data_ptr(), ssm_state.stride(0), positions.data_ptr(),
+                                         q_start.data_ptr(), state_slots.data_ptr(), y.data_ptr(), sequences, heads, groups,
+                                         n_state, head_dim, int(write_state), _stream()), "ssm_scan")

@@ -10,9 +10,9 @@ from .spec import ModelSpec
 
 def plain_or_none(pending):
     """A branch output that the stream does not hold yet, or None when it does (`Prenormed`) or there is none."""
-    from ..parts.base import Prenormed
+    from ..parts.base import Normed, Prenormed
 
-    return None if isinstance(pending, Prenormed) else pending
+    return None if isinstance(pending, (Prenormed, Normed)) else pending
 
 
 class Model:
@@ -79,7 +79,7 @@ class Model:
             if block.links_norms:        # the norm that reads the stream after this block
                 extra["next_norm"] = self.blocks[order[index + 1].layer].entry_norm if index + 1 < len(order) else self.final_norm
             pending = block.forward(stream, pending, ctx, storage.entries[self.cache_entry[index]],
-                                    self.writes_cache[index], **extra)
+                                    self.writes_cache[index] and not ctx.rehearsal, **extra)
         if ctx.observe:              # the reference norms every row before it gathers the wanted ones (qwen3.rs:228-233)
             ctx.observe("final_norm", self.final_norm.add_norm(stream, plain_or_none(pending), write_back=False))
         if ctx.want_rows is None:

@@ -8,8 +8,9 @@ import os
 from dataclasses import dataclass
 from typing import Callable
 
-from ..config.model_config import ModelConfig, Qwen3Config
+from ..config.model_config import ModelConfig, NiduvikConfig, Qwen3Config
 from ..errors import InvalidRequest
+from .niduvik import niduvik_spec
 from .qwen3 import qwen3_spec
 from .spec import ModelSpec
 
@@ -31,10 +32,14 @@ def register_architecture(model_type: str, config_class: type, spec: Callable[[M
 
 
 register_architecture("qwen3", Qwen3Config, qwen3_spec)
+register_architecture("niduvik", NiduvikConfig, niduvik_spec)
 
 
 def config_from_dict(raw: dict) -> ModelConfig:
+    """`model_type` names the architecture; a file without it may name its design under `architecture`."""
     model_type = raw.get("model_type")
+    if model_type is None and isinstance(raw.get("architecture"), str):
+        model_type = raw["architecture"].lower()
     if model_type not in ARCHITECTURES:
         raise InvalidRequest(f"unsupported model_type {model_type!r}; supported: {', '.join(sorted(ARCHITECTURES))}")
     return ARCHITECTURES[model_type].config_class.from_dict(raw)

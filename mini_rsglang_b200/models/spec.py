@@ -68,13 +68,13 @@ class ModelSpec:
         blocks = []
         for layer in self.layers:
             kind = BLOCKS.get(layer.block)
-            missing = [role for role in kind.roles if role not in layer.parts]
+            missing = [role for role in kind.roles if role not in layer.parts and role not in kind.optional_roles]
             unknown = [role for role in layer.parts if role not in kind.roles]
             if missing or unknown:
                 raise InvalidRequest(f"layer {layer.prefix!r}: block kind {layer.block!r} arranges {sorted(kind.roles)}; "
                                      f"missing {missing}, unknown {unknown}")
             parts = {role: registry.build(layer.parts[role], f"{layer.prefix}.{layer.names.get(role, role)}")
-                     for role, registry in kind.roles.items()}
+                     for role, registry in kind.roles.items() if role in layer.parts}
             blocks.append(kind(prefix=layer.prefix, **parts))
         final_norm = NORMS.build(self.final_norm, self.final_norm_prefix)
         head = HEADS.build(self.head, self.head_prefix)

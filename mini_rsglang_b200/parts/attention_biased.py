@@ -1,0 +1,153 @@
+"""Grouped-query attention without rotation, with what some designs put around its scores and values:
+
+  * biases on the q, k and v projections;
+  * key heads of `head_dim` and value heads of `value_dim` elements;
+  * a soft cap on the scaled scores, cap * tanh(score / cap), and after it a learned bias by the distance
+    i - j, taken from a small table through buckets: one row a distance below half the table, then rows spaced
+    evenly in the logarithm of the distance up to `bias_far`, the last row for everything beyond;
+  * a sliding window that also keeps the first `keep_first` positions in sight (at their true distances);
+  * a softmax with a sink: one more term of score 0 and no value in the denominator;
+  * values blended with those of the first layer that blends, (1 - m) v + m v_first per token; the blended values
+    are what the cache holds;
+  * an output gate, one sigmoid a (token, head), from the same input as the projections.
+
+One projection gives q | k | v | gate (float32 sums), one kernel adds the biases, blends, gates and writes the
+pages, one kernel attends.  Every constant is a parameter; none of the extras is tied to another."""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import kernels
+from ..errors import InvalidRequest
+from ..weights.spec import WeightSpec
+from .base import MIXERS, KVNeed, Mixer
+from .linear import linear
+
+
+def distance_buckets(rows: int, far: float) -> list[int]:
+    """Row of a bias table of `rows` rows for the distances 0, 1, ..., up to the first distance that takes the
+    last row (every larger one takes it too): n < rows // 2 -> n; else rows // 2 + floor(ln(n / half) /
+    ln(far / half) * (rows - half)), at most rows - 1.  Computed in float64 on the host."""
+    half = rows // 2
+    out = []
+    n = 0
+    while True:
+        if n < half:
+            b = n
+        else:
+            b = min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
+        out.append(b)
+        if b >= rows - 1 and n >= half:
+            return out
+        n += 1
+        if n > 1 << 22:
+            raise InvalidRequest("distance buckets: the last row is never reached")
+
+
+@MIXERS.register("biased_window_attention")
+class BiasedWindowAttention(Mixer):
+    replayable = True      # everything that changes from step to step is read from device tensors
+
+    def __init__(self, prefix: str, width: int, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int | None = None,
+                 scale: float | None = None, softcap: float = 0.0, window: int = 0, keep_first: int = 0,
+                 bias_rows: int = 0, bias_far: float = 0.0, sink: bool = False, projection_bias: bool = False,
+                 value_mix: str | None = None, value_mix_source: bool = False, output_gate: bool = False,
+                 names: dict | None = None):
+        """`value_mix`: a key under which the layers that blend values find the first one's values within a step
+        (None: no blending); `value_mix_source`: this layer is that first one (its own mixing weight is unused).
+        `names`: leaves of the tensors below the part's root."""
+        super().__init__(prefix)
+        if num_heads % num_kv_heads:
+            raise InvalidRequest("query heads must be a multiple of key/value heads")
+        self.width, self.nq, self.nkv, self.d = int(width), int(num_heads), int(num_kv_heads), int(head_dim)
+        self.e = int(value_dim) if value_dim else self.d
+        if not 0 < self.d <= 256 or not 0 < self.e <= 256:
+            raise InvalidRequest("head sizes must lie between 1 and 256")
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.d)
+        self.softcap, self.window, self.keep_first = float(softcap), int(window), int(keep_first)
+        self.bias_rows, self.bias_far, self.sink = int(bias_rows), float(bias_far), bool(sink)
+        if self.window < 0 or self.keep_first < 0 or self.softcap < 0:
+            raise InvalidRequest("window, kept first positions and soft cap cannot be negative")
+        # bias_rows -1: as many rows as the checkpoint's table has
+        if self.bias_rows > 0:
+            self._check_bias_table(self.bias_rows)
+        self.projection_bias, self.output_gate = bool(projection_bias), bool(output_gate)
+        self.value_mix, self.value_mix_source = value_mix, bool(value_mix_source)
+        self.leaf = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+                     "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias", "bias_table": "distance_bias",
+                     "mix": "value_mix", "gate": "gate_proj.weight"}
+        self.leaf.update(names or {})
+        self.fused = self.o = self.bias = self.distance_bias = None
+        self.mix = 0.0
+
+    def _check_bias_table(self, rows: int) -> None:
+        if rows < 2 or self.bias_far <= rows // 2:
+            raise InvalidRequest("a distance bias needs at least two rows and a far distance beyond half the table")
+
+    def weight_specs(self):
+        n = self.leaf
+        specs = [WeightSpec(self.name(n["q"]), (self.nq * self.d, self.width)),
+                 WeightSpec(self.name(n["k"]), (self.nkv * self.d, self.width)),
+                 WeightSpec(self.name(n["v"]), (self.nkv * self.e, self.width)),
+                 WeightSpec(self.name(n["o"]), (self.width, self.nq * self.e))]
+        if self.projection_bias:
+            specs += [WeightSpec(self.name(n["q_bias"]), (self.nq * self.d,), "bias"),
+                      WeightSpec(self.name(n["k_bias"]), (self.nkv * self.d,), "bias"),
+                      WeightSpec(self.name(n["v_bias"]), (self.nkv * self.e,), "bias")]
+        if self.bias_rows:
+            specs.append(WeightSpec(self.name(n["bias_table"]), (self.bias_rows, self.nq), "bias"))
+        if self.value_mix:
+            specs.append(WeightSpec(self.name(n["mix"]), (), "bias"))
+        if self.output_gate:
+            specs.append(WeightSpec(self.name(n["gate"]), (self.nq, self.width)))
+        return specs
+
+    def cache_need(self):
+        # A window that keeps first positions holds on to their pages: the group keeps every page.
+        kind = "window" if self.window and not self.keep_first else "full"
+        return KVNeed(self.nkv, self.d, kind, self.window if kind == "window" else 0, value_dim=self.e)
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        n = self.leaf
+        rows = [tensors[self.name(n[k])] for k in ("q", "k", "v")]
+        if self.output_gate:
+            rows.append(tensors[self.name(n["gate"])])
+        self.fused = torch.cat(rows, dim=0).contiguous()
+        self.o = tensors[self.name(n["o"])].contiguous()
+        if self.projection_bias:
+            self.bias = torch.cat([tensors[self.name(n[k])].float() for k in ("q_bias", "k_bias", "v_bias")]).contiguous()
+        if self.bias_rows:
+            table = tensors[self.name(n["bias_table"])].float()
+            self._check_bias_table(table.shape[0])
+            rows_of = torch.tensor(distance_buckets(table.shape[0], self.bias_far), dtype=torch.long, device=table.device)
+            self.distance_bias = table[rows_of].contiguous()         # [distances, heads]: the table, a row a distance
+        if self.value_mix and not self.value_mix_source:
+            self.mix = float(tensors[self.name(n["mix"])].float().item())
+
+    def forward(self, h, ctx, cache, write_cache=True):
+        tokens = h.shape[0]
+        device, dtype = self.o.device, self.runtime.dtype
+        proj = linear(h, self.fused, out_dtype=torch.float32)
+        q = torch.empty((tokens, self.nq * self.d), dtype=dtype, device=device)
+        gate = torch.empty((tokens, self.nq), dtype=torch.float32, device=device) if self.output_gate else None
+        v_first, mode = None, 0
+        if self.value_mix:
+            key = ("value_mix", self.value_mix)
+            if self.value_mix_source:
+                v_first = ctx.shared[key] = torch.empty((tokens, self.nkv * self.e), dtype=torch.float32, device=device)
+                mode = 1
+            else:
+                if key not in ctx.shared:
+                    raise InvalidRequest(f"{self.prefix}: no earlier layer of the step left values to blend with")
+                v_first, mode = ctx.shared[key], 2
+        kernels.qkv_bias_store(proj, self.bias, q, cache.k if write_cache else None, cache.v if write_cache else None,
+                               ctx.slots[cache.group] if write_cache else None, self.nq, self.nkv, self.d, self.e,
+                               v_first=v_first, mix_mode=mode, mix=self.mix, gate_out=gate)
+        out = torch.empty((tokens, self.nq * self.e), dtype=dtype, device=device)
+        kernels.attention_biased_simt(q, cache.k, cache.v, ctx.positions, ctx.seq_of_token, ctx.block_tables[cache.group], out,
+                                      self.nq, self.nkv, self.d, self.e, self.scale, self.softcap, self.window, self.keep_first,
+                                      self.distance_bias, gate, self.sink)
+        return linear(out, self.o, out_dtype=torch.float32)

@@ -66,6 +66,11 @@ class KVNeed:
     head_dim: int
     kind: str = "full"       # "full" | "window"
     window: int = 0
+    value_dim: int = 0       # elements of a value head where they differ from a key head's (0: head_dim)
+
+    @property
+    def v_head_dim(self) -> int:
+        return self.value_dim or self.head_dim
 
 
 @dataclass(frozen=True)
@@ -151,6 +156,20 @@ class Prenormed:
         return self.norm.add_norm(self.stream, None)
 
 
+@dataclass
+class Normed:
+    """Rows that the norm after a block has been run on already, by the kernel that added the block's last
+    branch to the stream: `rows` = norm(stream) in the engine's dtype.  The stream holds the sum."""
+
+    rows: torch.Tensor
+    norm: "Norm"
+    stream: torch.Tensor
+
+    @property
+    def shape(self):
+        return self.rows.shape
+
+
 def observing(ctx) -> bool:
     """Whether the step is watched layer by layer (`StepContext.observe`); a part asked without a context is not."""
     return getattr(ctx, "observe", None) is not None
@@ -158,6 +177,8 @@ def observing(ctx) -> bool:
 
 def plain(h):
     """`h` as a tensor."""
+    if isinstance(h, Normed):
+        return h.rows
     return h.materialise() if isinstance(h, Prenormed) else h
 
 
@@ -169,6 +190,9 @@ class Part:
         self.runtime: Runtime | None = None
 
     def name(self, leaf: str) -> str:
+        """The checkpoint name of a tensor of this part; an empty leaf names the part's root itself."""
+        if not leaf:
+            return self.prefix
         return f"{self.prefix}.{leaf}" if self.prefix else leaf
 
     def weight_specs(self) -> list[WeightSpec]:
@@ -252,16 +276,18 @@ class Block(Part):
     # role -> registry: the parts that this arrangement puts together, built in this order; every role is
     # also an attribute of the block.  The role `mixer`, if there is one, is the part that keeps a cache.
     roles: dict[str, "Registry"] = {}
+    optional_roles: tuple[str, ...] = ()     # roles that a layer may leave out (a layer without a feed-forward)
     entry_role: str | None = None    # the role of the norm that reads the stream first (a block before this one may link to it)
 
     def __init__(self, prefix: str, **parts: Part):
         super().__init__(prefix)
-        missing, unknown = [r for r in self.roles if r not in parts], [r for r in parts if r not in self.roles]
+        missing = [r for r in self.roles if r not in parts and r not in self.optional_roles]
+        unknown = [r for r in parts if r not in self.roles]
         if missing or unknown:
             raise InvalidRequest(f"block {type(self).__name__} at {prefix!r}: missing parts {missing}, unknown parts {unknown}")
-        self.parts = {role: parts[role] for role in self.roles}
-        for role, part in self.parts.items():
-            setattr(self, role, part)
+        self.parts = {role: parts[role] for role in self.roles if role in parts}
+        for role in self.roles:
+            setattr(self, role, self.parts.get(role))
 
     @property
     def entry_norm(self):

@@ -7,7 +7,11 @@ with few rows, the branch's last product adds it and the norm rides on the produ
 (`Prenormed` in parts/base.py)."""
 from __future__ import annotations
 
-from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, Prenormed, ResidualLink, observing, plain
+import torch
+
+from .. import kernels
+from ..errors import InvalidRequest
+from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, Normed, Prenormed, ResidualLink, observing, plain
 
 
 def _branch(part, h, stream, norm, *args):
@@ -43,3 +47,54 @@ class PreNormBlock(Block):
         f = self.feed_forward.forward(h, ctx)
         ctx.observe(f"{ctx.label}-output", stream + f.float())
         return f
+
+
+@BLOCKS.register("sandwich_norm")
+class SandwichNormBlock(Block):
+    """A norm before and a norm after each branch: x <- x + norm1b(mixer(norm1(x))), then, where the layer has a
+    feed-forward, x <- x + norm2b(feed_forward(norm2(x))).
+
+    The branches' last products leave float32 sums; one kernel norms a branch's output, adds it to the float32
+    stream and runs the norm that reads the stream next (`kernels.postnorm_add_norm`), so the sum and both
+    statistics are float32 and a layer's four norms are two launches.  What follows the block's last branch is the
+    next block's first norm: its rows are handed on as a `Normed`."""
+
+    links_norms = True
+    roles = {"norm1": NORMS, "mixer": MIXERS, "norm1b": NORMS, "norm2": NORMS, "feed_forward": FEED_FORWARDS, "norm2b": NORMS}
+    optional_roles = ("norm2", "feed_forward", "norm2b")
+    entry_role = "norm1"
+
+    def __init__(self, prefix: str, **parts):
+        super().__init__(prefix, **parts)
+        given = [self.parts.get(role) is not None for role in self.optional_roles]
+        if any(given) and not all(given):
+            raise InvalidRequest(f"block at {prefix!r}: a feed-forward comes with the norm before and the norm after it")
+        for role in ("norm1b", "norm2", "norm2b"):
+            norm = self.parts.get(role)
+            if norm is not None and not getattr(norm, "rides_on_products", False):
+                raise InvalidRequest(f"block at {prefix!r}: the norm {role!r} must be an RMS norm with float32 weights")
+
+    def _join(self, stream, branch, post, following):
+        """stream += post(branch); the rows of `following` (a norm, or None) over the sum."""
+        fused = following is not None and getattr(following, "rides_on_products", False)
+        if branch.dtype is not torch.float32:          # a branch written for another arrangement
+            branch = branch.float()
+        out = torch.empty(stream.shape, dtype=self.runtime.dtype, device=stream.device) if fused else None
+        kernels.postnorm_add_norm(stream, branch, post.weight, post.eps, following.weight if fused else None,
+                                  following.eps if fused else 0.0, out)
+        return Normed(out, following, stream) if fused else None
+
+    def forward(self, stream, pending, ctx, cache, write_cache=True, next_norm=None):
+        h = plain(self.norm1.add_norm(stream, pending))
+        if observing(ctx):
+            ctx.observe(f"{ctx.label}-input_norm", h)
+        a = self.mixer.forward(h, ctx, cache, write_cache)
+        if self.feed_forward is None:
+            pending = self._join(stream, a, self.norm1b, next_norm)
+        else:
+            h = self._join(stream, a, self.norm1b, self.norm2).rows
+            f = self.feed_forward.forward(h, ctx)
+            pending = self._join(stream, f, self.norm2b, next_norm)
+        if observing(ctx):
+            ctx.observe(f"{ctx.label}-output", stream.clone())
+        return pending

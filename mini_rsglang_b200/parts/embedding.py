@@ -13,17 +13,17 @@ from .linear import linear
 
 @EMBEDDINGS.register("token_embedding")
 class TokenEmbedding(Embedding):
-    def __init__(self, prefix: str, vocab: int, width: int):
+    def __init__(self, prefix: str, vocab: int, width: int, leaf: str = "weight"):
         super().__init__(prefix)
-        self.vocab, self.width = int(vocab), int(width)
+        self.vocab, self.width, self.leaf = int(vocab), int(width), leaf
         self.table = None
 
     def weight_specs(self):
-        return [WeightSpec(self.name("weight"), (self.vocab, self.width))]
+        return [WeightSpec(self.name(self.leaf), (self.vocab, self.width))]
 
     def bind(self, tensors, runtime):
         super().bind(tensors, runtime)
-        self.table = tensors[self.name("weight")]
+        self.table = tensors[self.name(self.leaf)]
 
     def forward(self, ctx) -> torch.Tensor:
         stream = torch.empty((ctx.num_tokens, self.width), dtype=torch.float32, device=self.table.device)

@@ -62,3 +62,35 @@ class SwiGLU(FeedForward):
         if observing(ctx):
             ctx.observe(f"{ctx.label}-swiglu", act)
         return linear(act, self.down, into=into)
+
+
+@FEED_FORWARDS.register("clamped_glu")
+class ClampedGLU(FeedForward):
+    """A gated feed-forward with clamped branches: g = min(gate(x), limit), u = clamp(up(x), -limit, limit),
+    down(g * sigmoid(alpha * g) * (u + 1)).  Gate and up are one projection over the row-concatenated matrices;
+    the result keeps the product's float32 sums (the norm that follows a branch reads them)."""
+
+    def __init__(self, prefix: str, width: int, inner: int, limit: float, alpha: float = 1.702, names: dict | None = None):
+        super().__init__(prefix)
+        self.width, self.inner, self.limit, self.alpha = int(width), int(inner), float(limit), float(alpha)
+        self.leaf = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
+        self.leaf.update(names or {})
+        self.gate_up = self.down = None
+
+    def weight_specs(self):
+        n = self.leaf
+        return [WeightSpec(self.name(n["gate"]), (self.inner, self.width)),
+                WeightSpec(self.name(n["up"]), (self.inner, self.width)),
+                WeightSpec(self.name(n["down"]), (self.width, self.inner))]
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        n = self.leaf
+        self.gate_up = torch.cat([tensors[self.name(n["gate"])], tensors[self.name(n["up"])]], dim=0).contiguous()
+        self.down = tensors[self.name(n["down"])].contiguous()
+
+    def forward(self, h, ctx):
+        h = plain(h)
+        act = torch.empty((h.shape[0], self.inner), dtype=self.runtime.dtype, device=self.down.device)
+        kernels.glu_clamped(linear(h, self.gate_up), act, self.limit, self.alpha)
+        return linear(act, self.down, out_dtype=torch.float32)

@@ -6,24 +6,25 @@ import torch
 
 from .. import kernels
 from ..weights.spec import WeightSpec
-from .base import NORMS, Norm, Prenormed
+from .base import NORMS, Norm, Normed, Prenormed
 
 
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
     rides_on_products = True
 
-    def __init__(self, prefix: str, width: int, eps: float):
+    def __init__(self, prefix: str, width: int, eps: float, leaf: str = "weight"):
         super().__init__(prefix)
         self.width, self.eps = int(width), float(eps)
+        self.leaf = leaf                   # the weights' name below the part's root ("": the root itself)
         self.weight: torch.Tensor | None = None
 
     def weight_specs(self):
-        return [WeightSpec(self.name("weight"), (self.width,), "vector")]
+        return [WeightSpec(self.name(self.leaf), (self.width,), "vector")]
 
     def bind(self, tensors, runtime):
         super().bind(tensors, runtime)
-        self.weight = tensors[self.name("weight")]
+        self.weight = tensors[self.name(self.leaf)]
 
     def forward(self, x):
         out = torch.empty_like(x)
@@ -34,6 +35,10 @@ class RMSNorm(Norm):
         if isinstance(delta, Prenormed):          # the stream holds the sum already
             if delta.norm is self and rows is None:
                 return delta                      # and the product after this norm finishes it
+            delta = None
+        if isinstance(delta, Normed):             # the stream holds the sum, and this norm of it may be there already
+            if delta.norm is self and rows is None:
+                return delta.rows
             delta = None
         n = residual.shape[0] if rows is None else rows.shape[0]
         out = torch.empty((n, self.width), dtype=self.runtime.dtype, device=residual.device)

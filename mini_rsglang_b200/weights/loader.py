@@ -54,7 +54,7 @@ def open_checkpoint(folder: str) -> dict[str, StoredTensor]:
 
 
 def held_dtype(role: str, engine_dtype: torch.dtype) -> torch.dtype:
-    if role == "vector":
+    if role in ("vector", "bias"):
         return torch.float32
     if role == "int_table":
         return torch.int32
@@ -83,7 +83,7 @@ def load_weights(folder: str, specs: Iterable[WeightSpec], engine_dtype: torch.d
         if name not in stored:
             continue
         t = stored[name]
-        if tuple(t.shape) != tuple(spec.shape):
+        if len(t.shape) != len(spec.shape) or any(want >= 0 and want != got for want, got in zip(spec.shape, t.shape)):
             wrong.append(f"{name}: shape {list(t.shape)}, expected {list(spec.shape)}")
         elif spec.role == "int_table" and t.dtype not in _INTS:
             wrong.append(f"{name}: dtype {t.dtype}, expected an integer table")

@@ -13,11 +13,13 @@ from typing import Iterable
 
 import torch
 
+from ..errors import InvalidRequest
 from .safetensors_io import write_safetensors
 from .spec import WeightSpec
 
 MATRIX_STD = 0.02
 VECTOR_STD = 0.05
+BIAS_STD = 0.5
 
 
 def _stream_seed(seed: int, name: str) -> int:
@@ -29,14 +31,18 @@ def random_tensor(spec: WeightSpec, seed: int, dtype: torch.dtype,
                   device: torch.device | str = "cpu") -> torch.Tensor:
     """One tensor of the seeded model.  Values drawn on the CPU and on a GPU differ (the
     generators differ); a folder written by `write_random_model` is drawn on the CPU."""
+    if any(n < 0 for n in spec.shape):
+        raise InvalidRequest(f"{spec.name}: a size that only a checkpoint states cannot be drawn; give it in the configuration")
     device = torch.device(device)
     gen = torch.Generator(device=device)
     gen.manual_seed(_stream_seed(seed, spec.name))
     if spec.role == "int_table":
         return torch.randint(0, 2**15, spec.shape, generator=gen, device=device, dtype=torch.int32)
-    values = torch.empty(spec.shape, dtype=torch.float32 if spec.role == "vector" else dtype, device=device)
+    values = torch.empty(spec.shape, dtype=torch.float32 if spec.role in ("vector", "bias") else dtype, device=device)
     if spec.role == "vector":
         values.normal_(1.0, VECTOR_STD, generator=gen)
+    elif spec.role == "bias":
+        values.normal_(0.0, BIAS_STD, generator=gen)
     else:
         values.normal_(0.0, MATRIX_STD, generator=gen)
     return values

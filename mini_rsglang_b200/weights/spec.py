@@ -11,7 +11,11 @@ class WeightSpec:
       (bfloat16 when serving, float32 on the 32-bit path); drawn N(0, 0.02);
     - "vector": a norm's scale; always held in float32 (widening bfloat16 is exact, a tensor
       stored in 32-bit stays so); drawn 1 + N(0, 0.05);
+    - "bias": a bias, a small table or a constant of a recurrence, wanted in full precision; always held in
+      float32; drawn N(0, 0.5);
     - "int_table": integers; held as int32.
+    A size of -1 in `shape` stands for "whatever the checkpoint has" (a table whose length only the file states);
+    seeded random weights cannot be drawn for such a spec.
     `optional_skip` names a tensor that may be present but is not used (a tied head)."""
 
     name: str
