@@ -93,6 +93,29 @@ def causal_conv(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor) -> to
     return out
 
 
+def selective_scan(x, B, C, dt_raw, dt_bias, A_log, D):
+    """x [T, heads, e], B and C [T, G, N], dt_raw [T, heads] -> y [T, heads, e]; the state starts at zero."""
+    T, heads, e = x.shape
+    G, N = B.shape[1], B.shape[2]
+    dt = torch.nn.functional.softplus(dt_raw + dt_bias, threshold=1e9)
+    decay = torch.exp(-torch.exp(A_log) * dt)
+    S = torch.zeros(heads, N, e, dtype=x.dtype)
+    y = torch.empty(T, heads, e, dtype=x.dtype)
+    for t in range(T):
+        for head in range(heads):
+            g = head // (heads // G)
+            S[head] = decay[t, head] * S[head] + dt[t, head] * torch.outer(B[t, g], x[t, head])
+            y[t, head] = S[head].T @ C[t, g] + D[head] * x[t, head]
+    return y
+
+
+def gated_part_norm(y, z, weight, parts, eps):
+    """(y * silu(z)), each of `parts` equal parts of a row by its own root mean square, times weight."""
+    T, inner = y.shape
+    g = y * silu(z)
+    return rms_norm(g.view(T, parts, inner // parts), None, eps).reshape(T, inner) * weight
+
+
 def mamba2_mixer(h, w, prefix, c, eps):
     """h [T, W] -> [T, W]: the recurrence token by token, state from zero."""
     heads, e, N, G = c["heads"], c["vdim"], c["state"], c["groups"]
@@ -104,26 +127,19 @@ def mamba2_mixer(h, w, prefix, c, eps):
     x = xbc[:, :inner].view(T, heads, e)
     B = xbc[:, inner:inner + G * N].view(T, G, N)
     C = xbc[:, inner + G * N:].view(T, G, N)
-    dt = torch.nn.functional.softplus(dt + w[prefix + "dt_bias"], threshold=1e9)      # [T, heads]
-    decay = torch.exp(-torch.exp(w[prefix + "A_log"]) * dt)
-    S = torch.zeros(heads, N, e, dtype=h.dtype)
-    y = torch.empty(T, heads, e, dtype=h.dtype)
-    for t in range(T):
-        for head in range(heads):
-            g = head // (heads // G)
-            S[head] = decay[t, head] * S[head] + dt[t, head] * torch.outer(B[t, g], x[t, head])
-            y[t, head] = S[head].T @ C[t, g] + w[prefix + "D"][head] * x[t, head]
-    y = y.reshape(T, inner) * silu(z)
-    parts = c["norm_groups"]
-    y = rms_norm(y.view(T, parts, inner // parts), None, eps).reshape(T, inner) * w[prefix + "norm"]
+    y = selective_scan(x, B, C, dt, w[prefix + "dt_bias"], w[prefix + "A_log"], w[prefix + "D"])
+    y = gated_part_norm(y.reshape(T, inner), z, w[prefix + "norm"], c["norm_groups"], eps)
     return y @ w[prefix + "o"].T
 
 
+def clamped_glu(g, u, limit, slope=1.702):
+    g = torch.clamp(g, max=limit)
+    u = torch.clamp(u, min=-limit, max=limit)
+    return g * torch.sigmoid(slope * g) * (u + 1.0)
+
+
 def feed_forward(h, w, prefix, c):
-    limit = c["limit"]
-    g = torch.clamp(h @ w[prefix + "gate"].T, max=limit)
-    u = torch.clamp(h @ w[prefix + "up"].T, min=-limit, max=limit)
-    return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ w[prefix + "down"].T
+    return clamped_glu(h @ w[prefix + "gate"].T, h @ w[prefix + "up"].T, c["limit"]) @ w[prefix + "down"].T
 
 
 def forward(config: dict, weights: dict, tokens, dtype=torch.float64):
