@@ -22,6 +22,7 @@ class Model:
         self.embedding, self.blocks, self.final_norm, self.head = spec.build_parts()
         for part in (self.embedding, *self.blocks, self.final_norm, self.head):
             part.bind(tensors, runtime)
+        self.final_norm.gathers_rows = True
         # cache entry that each run of the order reads; runs that borrow a cache write nothing
         self.cache_entry = [e.cache_of if e.cache_of is not None else i for i, e in enumerate(spec.run_order)]
         self.writes_cache = [e.cache_of is None for e in spec.run_order]

@@ -207,6 +207,10 @@ class Norm(Part):
     # True when the norm is y = x * rsqrt(mean(x^2) + eps) * weight with `weight` [width] float32, `width`
     # and `eps` as attributes: a product may then take over its arithmetic (see `Prenormed`).
     rides_on_products = False
+    # Set by the model on its last norm, which is run on the rows whose logits are wanted only: a block that could
+    # run the following norm in its own kernel leaves this one alone, so that a row's logits come from the same
+    # kernel whether all rows or some are wanted.
+    gathers_rows = False
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError

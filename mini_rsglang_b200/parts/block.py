@@ -76,7 +76,7 @@ class SandwichNormBlock(Block):
 
     def _join(self, stream, branch, post, following):
         """stream += post(branch); the rows of `following` (a norm, or None) over the sum."""
-        fused = following is not None and getattr(following, "rides_on_products", False)
+        fused = following is not None and getattr(following, "rides_on_products", False) and not following.gathers_rows
         if branch.dtype is not torch.float32:          # a branch written for another arrangement
             branch = branch.float()
         out = torch.empty(stream.shape, dtype=self.runtime.dtype, device=stream.device) if fused else None
