@@ -207,6 +207,117 @@ def continuous_run(args, torch, shape_name: str, cfg: dict, peak: dict) -> dict:
         "clocks": clocks, "impl": "ours"}
 
 
+HYBRID_SIZES = {
+    # width, feed-forward, query / key heads of 128 (Niduvik: values of 128 too), layers; the recurrence has 2 * width / 64
+    # heads of 64 with a state of 128 in 8 groups and 4 taps; the window is 1,024 with 4 kept tokens, the bias table 32 rows.
+    "1b": dict(width=2048, ff=8192, heads=16, kv_heads=4, layers=8),
+    "8b": dict(width=4096, ff=12288, heads=32, kv_heads=8, layers=8),
+}
+
+
+def hybrid_configs(size: dict, vocab: int = 32768):
+    """Niduvik at these layer sizes (two attention layers, then two recurrent ones, and so on) and the Qwen3 of equal
+    width, heads, feed-forward and depth."""
+    w = size["width"]
+    attention = {"type": "attention", "mlp": {"kind": "dense", "ff": size["ff"], "limit": 7.0},
+                 "mixer": {"heads": size["heads"], "kv_heads": size["kv_heads"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                           "softcap": 30.0, "bias_max": 4096.0, "bias_rows": 32, "v_mix": True, "mask": {"size": 1024, "keep_first": 4}}}
+    recurrent = {"type": "mamba2", "mlp": {"kind": "dense", "ff": size["ff"], "limit": 7.0},
+                 "mixer": {"heads": 2 * w // 64, "vdim": 64, "state": 128, "groups": 8, "conv": 4, "norm_groups": 8}}
+    layers = [attention if i % 4 < 2 else recurrent for i in range(size["layers"])]
+    niduvik = {"architecture": "Niduvik", "vocab": vocab, "width": w, "norm": {"eps": 1e-6}, "layers": layers}
+    qwen = dict(QWEN3_8B, hidden_size=w, intermediate_size=size["ff"], num_hidden_layers=size["layers"],
+                num_attention_heads=size["heads"], num_key_value_heads=size["kv_heads"], head_dim=128, vocab_size=vocab,
+                tie_word_embeddings=True, eos_token_id=1)
+    return niduvik, qwen
+
+
+def hybrid_run(args, torch, peak: dict) -> dict:
+    """`--design niduvik`: prefill of one prompt and decode steps of Niduvik at layer sizes of real models, beside the
+    Qwen3 of equal sizes, both with seeded random weights in bfloat16, timed on the device; with --kernel-shares each
+    model's kernels by their share of the device's time (standard error)."""
+    from mini_rsglang_b200 import RuntimeConfig, kernels
+    from mini_rsglang_b200.engine import EngineHandle, SequenceStep
+    from mini_rsglang_b200.models import config_from_dict
+
+    size = HYBRID_SIZES[args.size]
+    context, batch, prompt_len = args.context, args.batch, args.prompt
+    out = {"design": "Niduvik", "beside": "Qwen3 of equal width, heads, feed-forward and depth", "size": dict(size, name=args.size),
+           "batch": batch, "context": context, "prompt": prompt_len, "dtype": "bf16", "data": "synthetic: seeded random weights",
+           "peaks": peak}
+    gen = torch.Generator().manual_seed(7)
+    for name, raw in zip(("niduvik", "qwen3"), hybrid_configs(size)):
+        config = config_from_dict(raw)
+        page = 16
+        pages = batch * (-(-context // page)) + 2 * (-(-prompt_len // page)) + 8
+        limits = RuntimeConfig(max_seq_len=max(context, prompt_len), page_size=page, prefill_budget=prompt_len, max_running=max(batch, 2))
+        engine = EngineHandle.from_random(config, seed=1, dtype="bfloat16", config=limits, num_pages=pages)
+        runner = engine.runner
+        for entry in runner.storage.entries:
+            if entry.k is not None:
+                entry.k.normal_(0.0, 1.0)
+                entry.v.normal_(0.0, 1.0)
+        vocab = config.vocab_size
+
+        def timed(fn, repeat):
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            start.record()
+            for _ in range(repeat):
+                fn()
+            end.record()
+            torch.cuda.synchronize()
+            return start.elapsed_time(end)
+
+        prompt = torch.randint(0, vocab, (prompt_len,), generator=gen).tolist()
+
+        def prefill_once(request):
+            runner.cache.open(request)
+            runner.cache.extend(request, prompt_len)
+            runner.forward([SequenceStep(request, prompt, 0, [prompt_len - 1])])
+            torch.cuda.synchronize()
+            runner.cache.close(request)
+
+        samples = [timed(lambda r=r: prefill_once(10_000 + r), 1) for r in range(6)][3:]
+        prefill_ms = statistics.median(samples)
+        start_len = context - (args.warmup + args.steps)
+        ids = list(range(20_000, 20_000 + batch))
+        for r in ids:
+            runner.cache.open(r)
+            runner.cache.extend(r, start_len)
+        picked = torch.empty(batch, dtype=torch.int32, device=runner.device)
+        position = [start_len]
+
+        def one_step():
+            p = position[0]
+            for r in ids:
+                runner.cache.extend(r, p + 1)
+            tokens = torch.randint(0, vocab, (batch,), generator=gen).tolist()
+            logits = runner.forward([SequenceStep(r, [t], p, [0]) for r, t in zip(ids, tokens)])
+            kernels.argmax(logits, picked)
+            position[0] = p + 1
+
+        timed(one_step, args.warmup)
+        launches = kernels.launch_count
+        decode_ms = timed(one_step, args.steps) / args.steps
+        launches = (kernels.launch_count - launches) // args.steps
+        if args.kernel_shares:
+            print(f"--- {name}: one decode step at batch {batch}", file=sys.stderr)
+            kernel_shares(torch, one_step)
+            print(f"--- {name}: prefill of {prompt_len} tokens", file=sys.stderr)
+            kernel_shares(torch, lambda: prefill_once(30_000))
+        for r in ids:
+            runner.cache.close(r)
+        out[name] = {"prefill_tokens_per_s": round(prompt_len / prefill_ms * 1e3, 1), "prefill_ms": round(prefill_ms, 3),
+                     "decode_tokens_per_s": round(batch / decode_ms * 1e3, 1), "decode_ms_per_step": round(decode_ms, 4),
+                     "launches_per_decode_step": launches, "weight_bytes": runner.model.weight_bytes(),
+                     "decode_weight_read_frac": round(runner.model.weight_bytes() / (decode_ms * 1e-3) / 1e9 / peak["hbm_gbs"], 4)}
+        engine.shutdown()
+        del engine, runner
+        torch.cuda.empty_cache()
+    return out
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -224,6 +335,9 @@ def main() -> int:
     parser.add_argument("--output-tokens", type=int, default=64, help="--continuous: generated tokens a request")
     parser.add_argument("--prefill-budget", type=int, default=512, help="--continuous: tokens a step")
     parser.add_argument("--max-running", type=int, default=64, help="--continuous: requests in flight at most")
+    parser.add_argument("--design", choices=["niduvik"], help="Niduvik beside the Qwen3 of equal sizes (prefill and decode), instead of the default measurement")
+    parser.add_argument("--size", choices=sorted(HYBRID_SIZES), default="1b", help="--design: layer sizes")
+    parser.add_argument("--prompt", type=int, default=2048, help="--design: tokens of the prompt")
     parser.add_argument("--kernel-shares", action="store_true",
                         help="--continuous: after the timed wave, one more wave under torch.profiler; its kernels' shares of the "
                              "device's time go to standard error (not a timing)")
@@ -252,6 +366,9 @@ def main() -> int:
     layers = args.layers or full_layers
     cfg = dict(shape, num_hidden_layers=layers)
     peak = peaks()
+    if args.design:
+        print(json.dumps(hybrid_run(args, torch, peak)))
+        return 0
     if args.continuous:
         print(json.dumps(continuous_run(args, torch, shape_name, cfg, peak)))
         return 0
