@@ -1,0 +1,445 @@
+// The biased, windowed attention (see attention_biased.cu for the formulas) on the tensor cores: bfloat16 in,
+// float32 scores, softmax and sums; compiled for one pair of head sizes, -DMRS_HEAD_DIM=<keys> -DMRS_VALUE_DIM=<values>,
+// both multiples of 16 up to 256.
+//
+// As in attention_mma.cu a *tile* is a run of consecutive tokens of one request whose query rows are the pairs
+// (token, head within the group), so a key is read once for the whole group of query heads:
+//   rows mode (64 rows, 4 warps x 16 rows): prompt portions; every warp walks all key blocks of the tile;
+//   keys mode (16 rows shared by 4 warps):  decoded tokens and short portions; warp w takes keys 16w .. 16w + 15
+//                                           of every block of 64 and the four partial results are merged.
+// The keys a tile sees are two runs of blocks, those that hold kept first positions and those of the window; the
+// blocks between them are skipped, and what a single row sees is decided score by score.  K and V blocks are
+// gathered page by page with cp.async into two stages of shared memory; Q.K^T and P.V are mma.sync m16n8k16.
+// The sink (one more term exp(0) in the denominator) enters a row's running maximum and sum once.
+#include "common.cuh"
+
+#if !defined(MRS_HEAD_DIM) || !defined(MRS_VALUE_DIM)
+#error "compile with -DMRS_HEAD_DIM=<key head size> -DMRS_VALUE_DIM=<value head size>"
+#endif
+
+namespace {
+
+constexpr int D = MRS_HEAD_DIM, E = MRS_VALUE_DIM;
+static_assert(D % 16 == 0 && D >= 16 && D <= 256 && E % 16 == 0 && E >= 16 && E <= 256, "head sizes: multiples of 16 up to 256");
+constexpr int THREADS = 128;
+constexpr int ROWS_WIDE = 64, ROWS_NARROW = 16;
+constexpr int KV_WIDE = (D <= 128 && E <= 128) ? 64 : 32;
+constexpr int KV_NARROW = 64;
+constexpr float LOG2E = 1.4426950408889634f;
+
+template <int W> __device__ __forceinline__ int tile_offset(int row, int col) {      // element offset in a [rows][W] tile
+    const int chunk = col >> 3;
+    return row * W + (((W % 64 == 0) ? (chunk ^ (row & 7)) : chunk) << 3) + (col & 7);
+}
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_addr(dst)), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct Tile { int seq, first_token, tokens, pad; };
+
+struct Extras {            // what is put around the scores
+    const float* bias;     // [bias_rows, nq] by distance, the last row for every larger one; may be null
+    const float* gate;     // [tokens, nq], may be null
+    int bias_rows;
+    float scale, cap;      // cap 0: none
+    int window, keep_first, sink;
+};
+
+// Keys [key0, key0 + KV) of one kv head into a [KV][W] shared tile; rows at or beyond `key_end` or on a page that was
+// given back are zeros.
+template <int KV, int W>
+__device__ __forceinline__ void load_kv_block(bf16* dst, const bf16* __restrict__ cache, const int* __restrict__ pages, int key0,
+                                              int key_end, int kv_head, int nkv, int page_size, int page_shift) {
+    constexpr int CHUNKS = W / 8;
+    for (int idx = threadIdx.x; idx < KV * CHUNKS; idx += THREADS) {
+        const int row = idx / CHUNKS, chunk = idx % CHUNKS;
+        const int key = key0 + row;
+        bool valid = key < key_end;
+        const bf16* src = cache;
+        if (valid) {
+            const int page = pages[key >> page_shift];
+            valid = page >= 0;
+            if (valid) src = cache + (((size_t)page * nkv + kv_head) * page_size + (key & (page_size - 1))) * W + chunk * 8;
+        }
+        cp_async16(dst + row * W + (((W % 64 == 0) ? (chunk ^ (row & 7)) : chunk) << 3), src, valid);
+    }
+}
+
+template <int ROWS>
+__device__ __forceinline__ void load_q_tile(bf16* q_tile, const bf16* __restrict__ q, const Tile& tile, int rows, int group,
+                                            int kv_head, int nq) {
+    constexpr int CHUNKS = D / 8;
+    for (int idx = threadIdx.x; idx < ROWS * CHUNKS; idx += THREADS) {
+        const int row = idx / CHUNKS, chunk = idx % CHUNKS;
+        const bool valid = row < rows;
+        const bf16* src = q;
+        if (valid) src = q + ((size_t)(tile.first_token + row / group) * nq + kv_head * group + row % group) * D + chunk * 8;
+        cp_async16(q_tile + row * D + (((D % 64 == 0) ? (chunk ^ (row & 7)) : chunk) << 3), src, valid);
+    }
+}
+
+template <int NT>
+__device__ __forceinline__ void qk_product(float (&s)[NT][4], const bf16* q_tile, int q_row0, const bf16* k_tile, int key_row0) {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+        uint32_t a[4];
+        ldmatrix_x4(a, q_tile + tile_offset<D>(q_row0 + (lane & 15), kk * 16 + (lane >> 4) * 8));
+#pragma unroll
+        for (int nt = 0; nt < NT; nt += 2) {
+            uint32_t b[4];
+            ldmatrix_x4(b, k_tile + tile_offset<D>(key_row0 + nt * 8 + (lane & 7) + ((lane >> 4) << 3), kk * 16 + ((lane >> 3) & 1) * 8));
+            mma_bf16(s[nt], a, b[0], b[1]);
+            mma_bf16(s[nt + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+template <int NT>
+__device__ __forceinline__ void pv_product(float (&o)[E / 8][4], const float (&s)[NT][4], const bf16* v_tile, int key_row0) {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int kk = 0; kk < NT / 2; ++kk) {
+        uint32_t a[4];
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int dt = 0; dt < E / 8; dt += 2) {
+            uint32_t b[4];
+            ldmatrix_x4_trans(b, v_tile + tile_offset<E>(key_row0 + kk * 16 + (lane & 15), dt * 8 + (lane >> 4) * 8));
+            mma_bf16(o[dt], a, b[0], b[1]);
+            mma_bf16(o[dt + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+// Scales, caps, biases and masks the scores of one warp (in units of log 2 afterwards), updates the running maximum and
+// sum of its two rows (lane / 4 and lane / 4 + 8), rescales the accumulator and turns the scores into weights.
+template <int NT>
+__device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[E / 8][4], float (&row_max)[2], float (&row_sum)[2],
+                                             const int (&row_pos)[2], const int (&row_head)[2], int key0, int key_end, int nq,
+                                             const Extras& x) {
+    const int t = threadIdx.x & 3;
+    float block_max[2] = {-CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int key = key0 + nt * 8 + 2 * t + (e & 1);
+            const int pos = row_pos[e >> 1];
+            const int back = pos - key;
+            const bool seen = back >= 0 && key < key_end && (x.window <= 0 || back < x.window || key < x.keep_first);
+            float v = -CUDART_INF_F;
+            if (seen) {
+                v = s[nt][e] * x.scale;
+                if (x.cap > 0.0f) v = x.cap * tanhf(v / x.cap);
+                if (x.bias) v += x.bias[(size_t)min(back, x.bias_rows - 1) * nq + row_head[e >> 1]];
+                v *= LOG2E;
+            }
+            s[nt][e] = v;
+            block_max[e >> 1] = fmaxf(block_max[e >> 1], v);
+        }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        block_max[r] = fmaxf(block_max[r], __shfl_xor_sync(0xffffffffu, block_max[r], 1));
+        block_max[r] = fmaxf(block_max[r], __shfl_xor_sync(0xffffffffu, block_max[r], 2));
+        const float new_max = fmaxf(row_max[r], block_max[r]);
+        const float base = new_max == -CUDART_INF_F ? 0.0f : new_max;
+        const float alpha = exp2f(row_max[r] - base);
+        row_max[r] = new_max;
+        float sum = 0.0f;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            s[nt][2 * r] = exp2f(s[nt][2 * r] - base);
+            s[nt][2 * r + 1] = exp2f(s[nt][2 * r + 1] - base);
+            sum += s[nt][2 * r] + s[nt][2 * r + 1];
+        }
+        row_sum[r] = row_sum[r] * alpha + sum;      // the sum over the quad's lanes is taken at the end
+#pragma unroll
+        for (int dt = 0; dt < E / 8; ++dt) {
+            o[dt][2 * r] *= alpha;
+            o[dt][2 * r + 1] *= alpha;
+        }
+    }
+}
+
+// The key blocks of a tile, in units of KV positions: `kept` blocks from 0 on, then blocks [window_first, last).
+struct Blocks {
+    int kept, window_first, count;
+    __device__ __forceinline__ int at(int i) const { return i < kept ? i : window_first + (i - kept); }
+};
+__device__ __forceinline__ Blocks blocks_of(int first_pos, int key_end, int kv, const Extras& x) {
+    Blocks b;
+    const int key_begin = x.window > 0 ? max(0, first_pos - x.window + 1) : 0;
+    b.window_first = key_begin / kv;
+    const int kept_keys = x.window > 0 ? min(x.keep_first, key_begin) : 0;
+    b.kept = min((kept_keys + kv - 1) / kv, b.window_first);
+    b.count = b.kept + (key_end + kv - 1) / kv - b.window_first;
+    return b;
+}
+
+__global__ void __launch_bounds__(THREADS) attention_biased_rows_kernel(
+    const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, const int* __restrict__ positions,
+    const int* __restrict__ block_table, int table_width, const Tile* __restrict__ tiles, bf16* __restrict__ out, int nq, int nkv,
+    int page_size, int page_shift, Extras x) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);
+    bf16* k_tiles = q_tile + ROWS_WIDE * D;
+    bf16* v_tiles = k_tiles + 2 * KV_WIDE * D;
+    constexpr int NT = KV_WIDE / 8;
+
+    const Tile tile = tiles[blockIdx.x];
+    if (tile.tokens <= 0) return;
+    const int kv_head = blockIdx.y, group = nq / nkv;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int* pages = block_table + (size_t)tile.seq * table_width;
+    const int rows = tile.tokens * group;
+    load_q_tile<ROWS_WIDE>(q_tile, q, tile, rows, group, kv_head, nq);
+    const int first_pos = positions[tile.first_token], last_pos = positions[tile.first_token + tile.tokens - 1];
+    const int key_end = last_pos + 1;
+    const Blocks blocks = blocks_of(first_pos, key_end, KV_WIDE, x);
+
+    int row_pos[2], row_head[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = warp * 16 + (lane >> 2) + 8 * r;
+        row_pos[r] = row < rows ? positions[tile.first_token + row / group] : last_pos;
+        row_head[r] = kv_head * group + row % group;
+    }
+    float o[E / 8][4];
+#pragma unroll
+    for (int dt = 0; dt < E / 8; ++dt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[dt][e] = 0.0f;
+    float row_max[2], row_sum[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        row_max[r] = x.sink ? 0.0f : -CUDART_INF_F;
+        row_sum[r] = x.sink && (lane & 3) == 0 ? 1.0f : 0.0f;
+    }
+
+    if (blocks.count > 0) {
+        load_kv_block<KV_WIDE, D>(k_tiles, k_cache, pages, blocks.at(0) * KV_WIDE, key_end, kv_head, nkv, page_size, page_shift);
+        load_kv_block<KV_WIDE, E>(v_tiles, v_cache, pages, blocks.at(0) * KV_WIDE, key_end, kv_head, nkv, page_size, page_shift);
+    }
+    cp_async_commit();
+    for (int i = 0; i < blocks.count; ++i) {
+        const int stage = i & 1;
+        if (i + 1 < blocks.count) {
+            load_kv_block<KV_WIDE, D>(k_tiles + (stage ^ 1) * KV_WIDE * D, k_cache, pages, blocks.at(i + 1) * KV_WIDE, key_end, kv_head, nkv, page_size, page_shift);
+            load_kv_block<KV_WIDE, E>(v_tiles + (stage ^ 1) * KV_WIDE * E, v_cache, pages, blocks.at(i + 1) * KV_WIDE, key_end, kv_head, nkv, page_size, page_shift);
+        }
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const int key0 = blocks.at(i) * KV_WIDE;
+        const int warp_last_pos = __shfl_sync(0xffffffffu, row_pos[1], 28);
+        if (key0 <= warp_last_pos) {
+            float s[NT][4];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[nt][e] = 0.0f;
+            qk_product<NT>(s, q_tile, warp * 16, k_tiles + stage * KV_WIDE * D, 0);
+            softmax_step<NT>(s, o, row_max, row_sum, row_pos, row_head, key0, key_end, nq, x);
+            pv_product<NT>(o, s, v_tiles + stage * KV_WIDE * E, 0);
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float sum = row_sum[r];
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        const int row = warp * 16 + (lane >> 2) + 8 * r;
+        if (row >= rows) continue;
+        const int token = tile.first_token + row / group;
+        const float factor = (sum > 0.0f ? 1.0f / sum : 0.0f) * (x.gate ? x.gate[(size_t)token * nq + row_head[r]] : 1.0f);
+        bf16* dst = out + ((size_t)token * nq + row_head[r]) * E;
+#pragma unroll
+        for (int dt = 0; dt < E / 8; ++dt) {
+            const int col = dt * 8 + 2 * (lane & 3);
+            *reinterpret_cast<__nv_bfloat162*>(dst + col) = __floats2bfloat162_rn(o[dt][2 * r] * factor, o[dt][2 * r + 1] * factor);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(THREADS) attention_biased_keys_kernel(
+    const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, const int* __restrict__ positions,
+    const int* __restrict__ block_table, int table_width, const Tile* __restrict__ tiles, bf16* __restrict__ out, int nq, int nkv,
+    int page_size, int page_shift, Extras x) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);
+    bf16* k_tiles = q_tile + ROWS_NARROW * D;
+    bf16* v_tiles = k_tiles + 2 * KV_NARROW * D;
+    constexpr int NT = 2;
+
+    const Tile tile = tiles[blockIdx.x];
+    if (tile.tokens <= 0) return;
+    const int kv_head = blockIdx.y, group = nq / nkv;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int* pages = block_table + (size_t)tile.seq * table_width;
+    const int rows = tile.tokens * group;
+    load_q_tile<ROWS_NARROW>(q_tile, q, tile, rows, group, kv_head, nq);
+    const int first_pos = positions[tile.first_token], last_pos = positions[tile.first_token + tile.tokens - 1];
+    const int key_end = last_pos + 1;
+    const Blocks blocks = blocks_of(first_pos, key_end, KV_NARROW, x);
+
+    int row_pos[2], row_head[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = (lane >> 2) + 8 * r;
+        row_pos[r] = row < rows ? positions[tile.first_token + row / group] : last_pos;
+        row_head[r] = kv_head * group + row % group;
+    }
+    float o[E / 8][4];
+#pragma unroll
+    for (int dt = 0; dt < E / 8; ++dt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[dt][e] = 0.0f;
+    float row_max[2] = {-CUDART_INF_F, -CUDART_INF_F}, row_sum[2] = {0.0f, 0.0f};
+
+    if (blocks.count > 0) {
+        load_kv_block<KV_NARROW, D>(k_tiles, k_cache, pages, blocks.at(0) * KV_NARROW, key_end, kv_head, nkv, page_size, page_shift);
+        load_kv_block<KV_NARROW, E>(v_tiles, v_cache, pages, blocks.at(0) * KV_NARROW, key_end, kv_head, nkv, page_size, page_shift);
+    }
+    cp_async_commit();
+    for (int i = 0; i < blocks.count; ++i) {
+        const int stage = i & 1;
+        if (i + 1 < blocks.count) {
+            load_kv_block<KV_NARROW, D>(k_tiles + (stage ^ 1) * KV_NARROW * D, k_cache, pages, blocks.at(i + 1) * KV_NARROW, key_end, kv_head, nkv, page_size, page_shift);
+            load_kv_block<KV_NARROW, E>(v_tiles + (stage ^ 1) * KV_NARROW * E, v_cache, pages, blocks.at(i + 1) * KV_NARROW, key_end, kv_head, nkv, page_size, page_shift);
+        }
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const int key0 = blocks.at(i) * KV_NARROW + warp * 16;
+        if (key0 < key_end) {
+            float s[NT][4];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[nt][e] = 0.0f;
+            qk_product<NT>(s, q_tile, 0, k_tiles + stage * KV_NARROW * D, warp * 16);
+            softmax_step<NT>(s, o, row_max, row_sum, row_pos, row_head, key0, key_end, nq, x);
+            pv_product<NT>(o, s, v_tiles + stage * KV_NARROW * E, warp * 16);
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    // merge the four warps through shared memory: [4][16][E] sums and [4][16][2] (maximum, sum); the sink joins here
+    float* merge_o = reinterpret_cast<float*>(k_tiles);
+    float* merge_ml = merge_o + 4 * ROWS_NARROW * E;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float sum = row_sum[r];
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        const int row = (lane >> 2) + 8 * r;
+        if ((lane & 3) == 0) {
+            merge_ml[(warp * ROWS_NARROW + row) * 2] = row_max[r];
+            merge_ml[(warp * ROWS_NARROW + row) * 2 + 1] = sum;
+        }
+#pragma unroll
+        for (int dt = 0; dt < E / 8; ++dt) {
+            const int col = dt * 8 + 2 * (lane & 3);
+            merge_o[(warp * ROWS_NARROW + row) * E + col] = o[dt][2 * r];
+            merge_o[(warp * ROWS_NARROW + row) * E + col + 1] = o[dt][2 * r + 1];
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < ROWS_NARROW * E; idx += THREADS) {
+        const int row = idx / E, col = idx % E;
+        if (row >= rows) continue;
+        float m = x.sink ? 0.0f : -CUDART_INF_F;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) m = fmaxf(m, merge_ml[(w * ROWS_NARROW + row) * 2]);
+        const float base = m == -CUDART_INF_F ? 0.0f : m;
+        float sum = x.sink ? exp2f(-base) : 0.0f, acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float f = exp2f(merge_ml[(w * ROWS_NARROW + row) * 2] - base);
+            sum += merge_ml[(w * ROWS_NARROW + row) * 2 + 1] * f;
+            acc += merge_o[(w * ROWS_NARROW + row) * E + col] * f;
+        }
+        const int token = tile.first_token + row / group, head = kv_head * group + row % group;
+        const float factor = (sum > 0.0f ? 1.0f / sum : 0.0f) * (x.gate ? x.gate[(size_t)token * nq + head] : 1.0f);
+        out[((size_t)token * nq + head) * E + col] = __float2bfloat16_rn(acc * factor);
+    }
+}
+
+constexpr size_t smem_rows = (size_t)(ROWS_WIDE * D + 2 * KV_WIDE * (D + E)) * sizeof(bf16);
+constexpr size_t smem_keys_tiles = (size_t)(ROWS_NARROW * D + 2 * KV_NARROW * (D + E)) * sizeof(bf16);
+constexpr size_t smem_keys_merge = (size_t)ROWS_NARROW * D * sizeof(bf16) + (size_t)(4 * ROWS_NARROW * E + 4 * ROWS_NARROW * 2) * sizeof(float);
+constexpr size_t smem_keys = smem_keys_tiles > smem_keys_merge ? smem_keys_tiles : smem_keys_merge;
+
+int page_shift_of(int page_size) {
+    int shift = 0;
+    while ((1 << shift) < page_size) ++shift;
+    return (1 << shift) == page_size ? shift : -1;
+}
+
+}  // namespace
+
+MRS_EXPORT int mrs_attention_biased_mma_key_dim() { return D; }
+MRS_EXPORT int mrs_attention_biased_mma_value_dim() { return E; }
+
+// narrow != 0: tiles of up to 16 / group tokens (keys mode); else tiles of up to 64 / group tokens (rows mode).
+MRS_EXPORT int mrs_attention_biased_mma(int narrow, const void* q, const void* k_cache, const void* v_cache, const int* positions,
+                                        const int* block_table, int table_width, const int* tiles, int num_tiles, void* out,
+                                        const float* bias, int bias_rows, const float* gate, int nq, int nkv, int page_size,
+                                        float scale, float cap, int window, int keep_first, int sink, void* stream) {
+    if (num_tiles <= 0) return 0;
+    const int shift = page_shift_of(page_size);
+    if (shift < 0 || nkv <= 0 || nq % nkv || nq / nkv > (narrow ? ROWS_NARROW : ROWS_WIDE) || (bias && bias_rows <= 0) || window < 0 ||
+        keep_first < 0)
+        return MRS_BAD_ARGUMENT;
+    Extras x;
+    x.bias = bias, x.gate = gate, x.bias_rows = bias_rows, x.scale = scale, x.cap = cap, x.window = window, x.keep_first = keep_first;
+    x.sink = sink;
+    static bool configured[2] = {false, false};
+    if (!configured[narrow ? 1 : 0]) {
+        cudaError_t e = narrow
+            ? cudaFuncSetAttribute(attention_biased_keys_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_keys)
+            : cudaFuncSetAttribute(attention_biased_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_rows);
+        if (e != cudaSuccess) return (int)e;
+        configured[narrow ? 1 : 0] = true;
+    }
+    if (narrow)
+        MRS_LAUNCH(attention_biased_keys_kernel, dim3(num_tiles, nkv), THREADS, smem_keys, stream, (const bf16*)q, (const bf16*)k_cache,
+                   (const bf16*)v_cache, positions, block_table, table_width, (const Tile*)tiles, (bf16*)out, nq, nkv, page_size, shift, x);
+    else
+        MRS_LAUNCH(attention_biased_rows_kernel, dim3(num_tiles, nkv), THREADS, smem_rows, stream, (const bf16*)q, (const bf16*)k_cache,
+                   (const bf16*)v_cache, positions, block_table, table_width, (const Tile*)tiles, (bf16*)out, nq, nkv, page_size, shift, x);
+    MRS_RETURN_LAUNCH_STATUS();
+}

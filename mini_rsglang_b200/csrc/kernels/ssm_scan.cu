@@ -96,37 +96,52 @@ MRS_EXPORT int mrs_causal_conv_silu(const float* in, int in_stride, int offset, 
 }
 
 // ---------------------------------------------------------------------------------------------
-// The recurrence, token by token.  One block per (sequence, head); thread (p, s): column p of S and the rows
-// n = s * per + i of it in registers (lanes of one p are neighbours, so that y's sum over n is a few shuffles).
+// The recurrence, token by token.  One block per (sequence, head, slice of the head's columns); thread (p, s): column p
+// of S and the rows n = s * per + i of it in registers (lanes of one p are neighbours, so that y's sum over n is a few shuffles).
 // xbc [tokens, heads * P + 2 * groups * N] float32 (x | B | C after convolution and silu), raw dt a column range of
 // the projection's rows, y [tokens, heads * P] float32.  ssm_state [slots, heads, N, P].
 // The loads of the next token are issued before the arithmetic of this one.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.0f) + log1pf(expf(-fabsf(x))); }
 
+// WHOLE: a sequence's rows in one go, from the slot's state to the slot's state.  For long portions the rows are cut
+// into chunks of `chunk_len` that run side by side in three passes: LOCAL runs every chunk from a zero state and leaves
+// its end state and the product of its decays in scratch; `ssm_chunk_states_kernel` walks a sequence's chunks once,
+// turning the local end states into the true state at every chunk's start (and the slot's new state); FINAL runs every
+// chunk again from that state and writes y.
+enum { SSM_WHOLE = 0, SSM_LOCAL = 1, SSM_FINAL = 2 };
+
+template <int MODE>
 __global__ void ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt_in, int dt_stride,
                                 const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
                                 float* __restrict__ ssm_state, long long state_stride, const int* __restrict__ positions,
                                 const int* __restrict__ q_start, const int* __restrict__ state_slots, float* __restrict__ y,
-                                int heads, int groups, int N, int P, int lanes_per_column, int per, int write_state) {
+                                int heads, int groups, int N, int P, int lanes_per_column, int per, int write_state,
+                                float* __restrict__ chunk_state, float* __restrict__ chunk_decay, int chunk_len, int max_chunks,
+                                int slices, int columns) {
     pdl_launch_dependents();
     pdl_wait();
-    const int seq = blockIdx.x, head = blockIdx.y;
-    const int start_row = q_start[seq], end_row = q_start[seq + 1];
+    const int seq = blockIdx.x, head = blockIdx.y / slices, slice = blockIdx.y % slices, chunk = blockIdx.z;
+    const int seq_start = q_start[seq], seq_end = q_start[seq + 1];
     const int slot = state_slots[seq];
-    if (slot < 0 || end_row <= start_row) return;
-    const int s = threadIdx.x % lanes_per_column, p = threadIdx.x / lanes_per_column;
-    const bool live = p < P;
+    if (slot < 0 || seq_end <= seq_start) return;
+    const int start_row = MODE == SSM_WHOLE ? seq_start : seq_start + chunk * chunk_len;
+    const int end_row = MODE == SSM_WHOLE ? seq_end : min(seq_end, start_row + chunk_len);
+    if (start_row >= end_row) return;
+    const int s = threadIdx.x % lanes_per_column, p = slice * columns + threadIdx.x / lanes_per_column;
+    const bool live = p < P && (int)threadIdx.x / lanes_per_column < columns;
     const int group = head / (heads / groups);
     const int inner = heads * P, row_width = inner + 2 * groups * N;
     const int n0 = s * per;
-    float* state = ssm_state + (long long)slot * state_stride + (size_t)head * N * P;
+    float* state = MODE == SSM_WHOLE ? ssm_state + (long long)slot * state_stride + (size_t)head * N * P
+                                     : chunk_state + (((size_t)seq * heads + head) * max_chunks + chunk) * N * P;
     float S[SSM_PER_LANE];
-    const bool fresh = positions[start_row] == 0;
+    const bool zero = MODE == SSM_LOCAL || (MODE == SSM_WHOLE && positions[seq_start] == 0);
 #pragma unroll
     for (int i = 0; i < SSM_PER_LANE; ++i)
-        S[i] = (!fresh && live && i < per && n0 + i < N) ? state[(size_t)(n0 + i) * P + p] : 0.0f;
+        S[i] = (!zero && live && i < per && n0 + i < N) ? state[(size_t)(n0 + i) * P + p] : 0.0f;
     const float bias = dt_bias[head], rate = -expf(a_log[head]), skip = d_skip[head];
+    float decays = 1.0f;
 
     float b_next[SSM_PER_LANE], c_next[SSM_PER_LANE], x_next = 0.0f, dt_next = 0.0f;
     auto load = [&](int row) {
@@ -137,7 +152,7 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, const float* __re
         for (int i = 0; i < SSM_PER_LANE; ++i) {
             const bool in = i < per && n0 + i < N;
             b_next[i] = in ? r[inner + group * N + n0 + i] : 0.0f;
-            c_next[i] = in ? r[inner + groups * N + group * N + n0 + i] : 0.0f;
+            if (MODE != SSM_LOCAL) c_next[i] = in ? r[inner + groups * N + group * N + n0 + i] : 0.0f;
         }
     };
     load(start_row);
@@ -145,38 +160,99 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, const float* __re
         float b[SSM_PER_LANE], c[SSM_PER_LANE];
         const float x = x_next, dt = softplus_f(dt_next + bias);
 #pragma unroll
-        for (int i = 0; i < SSM_PER_LANE; ++i) b[i] = b_next[i], c[i] = c_next[i];
+        for (int i = 0; i < SSM_PER_LANE; ++i) {
+            b[i] = b_next[i];
+            if (MODE != SSM_LOCAL) c[i] = c_next[i];
+        }
         if (row + 1 < end_row) load(row + 1);
         const float decay = expf(rate * dt), dx = dt * x;
+        if (MODE == SSM_LOCAL) decays *= decay;
         float sum = 0.0f;
 #pragma unroll
         for (int i = 0; i < SSM_PER_LANE; ++i) {
             S[i] = decay * S[i] + dx * b[i];
-            sum += S[i] * c[i];
+            if (MODE != SSM_LOCAL) sum += S[i] * c[i];
         }
-        for (int o = 1; o < lanes_per_column; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        if (live && s == 0) y[(size_t)row * inner + head * P + p] = sum + skip * x;
+        if (MODE != SSM_LOCAL) {
+            for (int o = 1; o < lanes_per_column; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if (live && s == 0) y[(size_t)row * inner + head * P + p] = sum + skip * x;
+        }
     }
-    if (write_state && live) {
+    if (MODE == SSM_LOCAL && threadIdx.x == 0 && slice == 0) chunk_decay[((size_t)seq * heads + head) * max_chunks + chunk] = decays;
+    if ((MODE == SSM_LOCAL || (MODE == SSM_WHOLE && write_state)) && live) {
 #pragma unroll
         for (int i = 0; i < SSM_PER_LANE; ++i)
             if (i < per && n0 + i < N) state[(size_t)(n0 + i) * P + p] = S[i];
     }
 }
 
+// One thread an element of a (sequence, head)'s state: chunk c's entry of `chunk_state` goes from the chunk's local end
+// state to the state at its start, S_in[0] = the slot's state (zero at position 0), S_in[c + 1] = decay_c S_in[c] + local_c.
+__global__ void ssm_chunk_states_kernel(float* __restrict__ ssm_state, long long state_stride, const int* __restrict__ positions,
+                                        const int* __restrict__ q_start, const int* __restrict__ state_slots,
+                                        float* __restrict__ chunk_state, const float* __restrict__ chunk_decay, int heads, int elements,
+                                        int chunk_len, int max_chunks, int write_state) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int seq = blockIdx.x, head = blockIdx.y;
+    const int seq_start = q_start[seq], rows = q_start[seq + 1] - seq_start;
+    const int slot = state_slots[seq];
+    if (slot < 0 || rows <= 0) return;
+    const int chunks = (rows + chunk_len - 1) / chunk_len;
+    const bool fresh = positions[seq_start] == 0;
+    float* state = ssm_state + (long long)slot * state_stride + (size_t)head * elements;
+    float* local = chunk_state + ((size_t)seq * heads + head) * max_chunks * elements;
+    const float* decay = chunk_decay + ((size_t)seq * heads + head) * max_chunks;
+    for (int i = blockIdx.z * blockDim.x + threadIdx.x; i < elements; i += gridDim.z * blockDim.x) {
+        float value = fresh ? 0.0f : state[i];
+        for (int c = 0; c < chunks; ++c) {
+            const float end = local[(size_t)c * elements + i];
+            local[(size_t)c * elements + i] = value;
+            value = decay[c] * value + end;
+        }
+        if (write_state) state[i] = value;
+    }
+}
+
+// `chunk_len` 0: every sequence in one go.  Otherwise the three passes over chunks of that many rows; `scratch` then holds
+// sequences * heads * max_chunks * (N * P + 1) floats, max_chunks = ceil(tokens / chunk_len).
 MRS_EXPORT int mrs_ssm_scan(const float* xbc, const float* dt_in, int dt_stride, const float* dt_bias, const float* a_log,
                             const float* d_skip, float* ssm_state, long long state_stride, const int* positions, const int* q_start,
-                            const int* state_slots, float* y, int sequences, int heads, int groups, int N, int P, int write_state,
-                            void* stream) {
-    if (sequences <= 0) return 0;
-    if (heads <= 0 || groups <= 0 || heads % groups || N <= 0 || P <= 0) return MRS_BAD_ARGUMENT;
+                            const int* state_slots, float* y, int tokens, int sequences, int heads, int groups, int N, int P,
+                            int write_state, int chunk_len, float* scratch, void* stream) {
+    if (sequences <= 0 || tokens <= 0) return 0;
+    if (heads <= 0 || groups <= 0 || heads % groups || N <= 0 || P <= 0 || chunk_len < 0 || (chunk_len > 0 && !scratch))
+        return MRS_BAD_ARGUMENT;
     int lanes = 1;
     while (lanes < 32 && (N + lanes - 1) / lanes > SSM_PER_LANE) lanes <<= 1;
     const int per = (N + lanes - 1) / lanes;
     if (per > SSM_PER_LANE) return MRS_BAD_ARGUMENT;                 // N above 512
-    const int threads = (P * lanes + 31) / 32 * 32;
-    if (threads > 1024) return MRS_BAD_ARGUMENT;
-    MRS_LAUNCH(ssm_scan_kernel, dim3(sequences, heads), threads, 0, stream, xbc, dt_in, dt_stride, dt_bias, a_log, d_skip, ssm_state,
-               state_stride, positions, q_start, state_slots, y, heads, groups, N, P, lanes, per, write_state);
+    // blocks of about 128 threads, each a slice of a head's columns: several blocks share an SM and hide one another's waits
+    int columns = 128 / lanes;
+    if (columns > P) columns = P;
+    const int slices = (P + columns - 1) / columns;
+    const int threads = (columns * lanes + 31) / 32 * 32;
+    if ((long long)heads * slices > 65535) return MRS_BAD_ARGUMENT;
+    if (chunk_len == 0) {
+        MRS_LAUNCH(ssm_scan_kernel<SSM_WHOLE>, dim3(sequences, heads * slices), threads, 0, stream, xbc, dt_in, dt_stride, dt_bias, a_log, d_skip,
+                   ssm_state, state_stride, positions, q_start, state_slots, y, heads, groups, N, P, lanes, per, write_state,
+                   (float*)nullptr, (float*)nullptr, 0, 0, slices, columns);
+        MRS_RETURN_LAUNCH_STATUS();
+    }
+    const int max_chunks = (tokens + chunk_len - 1) / chunk_len;
+    if (max_chunks > 65535) return MRS_BAD_ARGUMENT;
+    float* chunk_state = scratch;
+    float* chunk_decay = scratch + (size_t)sequences * heads * max_chunks * N * P;
+    MRS_LAUNCH(ssm_scan_kernel<SSM_LOCAL>, dim3(sequences, heads * slices, max_chunks), threads, 0, stream, xbc, dt_in, dt_stride, dt_bias, a_log,
+               d_skip, ssm_state, state_stride, positions, q_start, state_slots, y, heads, groups, N, P, lanes, per, write_state,
+               chunk_state, chunk_decay, chunk_len, max_chunks, slices, columns);
+    const int elements = N * P;
+    int element_blocks = (elements + 255) / 256;
+    if (element_blocks > 64) element_blocks = 64;
+    MRS_LAUNCH(ssm_chunk_states_kernel, dim3(sequences, heads, element_blocks), 256, 0, stream, ssm_state, state_stride, positions, q_start,
+               state_slots, chunk_state, (const float*)chunk_decay, heads, elements, chunk_len, max_chunks, write_state);
+    MRS_LAUNCH(ssm_scan_kernel<SSM_FINAL>, dim3(sequences, heads * slices, max_chunks), threads, 0, stream, xbc, dt_in, dt_stride, dt_bias, a_log,
+               d_skip, ssm_state, state_stride, positions, q_start, state_slots, y, heads, groups, N, P, lanes, per, write_state,
+               chunk_state, chunk_decay, chunk_len, max_chunks, slices, columns);
     MRS_RETURN_LAUNCH_STATUS();
 }

@@ -1027,7 +1027,7 @@ _HYBRID_SIGNATURES = {
     "mrs_causal_conv_silu": [_c_vp, _c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_ll, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int,
                              _c_int, _c_int, _c_int, _c_vp],
     "mrs_ssm_scan": [_c_vp, _c_vp, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_ll, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int,
-                     _c_int, _c_int, _c_int, _c_vp],
+                     _c_int, _c_int, _c_int, _c_int, _c_int, _c_vp, _c_vp],
 }
 _hybrid_lib = None
 
@@ -1176,11 +1176,16 @@ def causal_conv_silu(proj: torch.Tensor, offset: int, weight: torch.Tensor, bias
 
 
 def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dt_bias, a_log, d_skip, ssm_state: torch.Tensor, positions, q_start, state_slots,
-             y: torch.Tensor, heads: int, groups: int, n_state: int, head_dim: int, write_state: bool = True) -> None:
+             y: torch.Tensor, heads: int, groups: int, n_state: int, head_dim: int, write_state: bool = True,
+             chunk_len: int | None = None) -> None:
     """The recurrence S_t = exp(-exp(A_log) dt_t) S_(t-1) + dt_t B_t x_t^T, y_t = S_t^T C_t + D x_t with dt_t =
     softplus(raw + dt_bias), per (sequence, head), token by token in float32.  `xbc` [tokens, heads * P + 2 * groups * N]
     float32 holds x | B | C; `dt` the raw step sizes (a column range of wider float32 rows); `ssm_state`
-    [slots, heads, N, P] float32 (a view: dense within a slot); a sequence that starts at position 0 starts from zero."""
+    [slots, heads, N, P] float32 (a view: dense within a slot); a sequence that starts at position 0 starts from zero.
+    `chunk_len` 0: every sequence in one go; n > 0: chunks of n rows side by side in three passes (local states, the
+    states at the chunks' starts, the outputs); None: chosen from the step's shapes, chunks where long portions of few
+    sequences would leave most of the GPU idle."""
+    global launch_count
     tokens = xbc.shape[0]
     inner = heads * head_dim
     _need(xbc, torch.float32, "x|B|C", (tokens, inner + 2 * groups * n_state))
@@ -1193,7 +1198,87 @@ def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dt_bias, a_log, d_skip, ssm_st
         raise InvalidRequest("ssm_scan: the state must be float32 [slots, heads, N, P], dense within a slot")
     _need(y, torch.float32, "recurrence output", (tokens, inner))
     sequences = state_slots.shape[0]
+    if chunk_len is None:
+        chunk_len = ssm_chunk_length(tokens, sequences, heads, n_state, head_dim, sm_count(xbc.device))
+    scratch = None
+    if chunk_len:
+        chunks = -(-tokens // chunk_len)
+        scratch = attention_scratch(xbc.device, sequences * heads * chunks * (n_state * head_dim + 1), lane=2)
+        launch_count += 2
     _check(hybrid_library().mrs_ssm_scan(xbc.data_ptr(), dt.data_ptr(), dt.stride(0), dt_bias.data_ptr(), a_log.data_ptr(),
                                          d_skip.data_ptr(), ssm_state.data_ptr(), ssm_state.stride(0), positions.data_ptr(),
-                                         q_start.data_ptr(), state_slots.data_ptr(), y.data_ptr(), sequences, heads, groups,
-                                         n_state, head_dim, int(write_state), _stream()), "ssm_scan")
+                                         q_start.data_ptr(), state_slots.data_ptr(), y.data_ptr(), tokens, sequences, heads, groups,
+                                         n_state, head_dim, int(write_state), int(chunk_len), _ptr(scratch), _stream()), "ssm_scan")
+
+
+def ssm_chunk_length(tokens: int, sequences: int, heads: int, n_state: int, head_dim: int, sms: int) -> int:
+    """Rows of a chunk of the recurrence, 0 for none, from a step's shapes alone (a recorded step keeps its choice): chunks
+    pay twice the arithmetic for blocks that run side by side, so they are taken where the sequences' own blocks (one a
+    head and slice of 128 threads, four to an SM) fill less than half of the GPU and the portions are long."""
+    lanes = 1
+    while lanes < 32 and -(-n_state // lanes) > 16:
+        lanes *= 2
+    slices = -(-head_dim // max(1, min(128 // lanes, head_dim)))
+    blocks = sequences * heads * slices
+    room = 4 * sms
+    if tokens < 512 or tokens < 128 * sequences or 2 * blocks > room:
+        return 0
+    chunks = min(room // blocks, tokens // 64)
+    if chunks < 2:
+        return 0
+    rows = -(-tokens // chunks)
+    return -(-rows // 64) * 64
+
+
+_biased_mma_libs: dict[tuple, ctypes.CDLL] = {}
+
+
+def attention_biased_mma_supported(d: int, e: int, group: int, page_size: int) -> bool:
+    """Head sizes that are multiples of 16 up to 256, groups of up to 64 query heads, pages of a power of two."""
+    return (d % 16 == 0 and e % 16 == 0 and 16 <= d <= 256 and 16 <= e <= 256 and group <= MMA_ROWS_WIDE
+            and page_size & (page_size - 1) == 0)
+
+
+def attention_biased_mma_library(d: int, e: int) -> ctypes.CDLL:
+    """The tensor-core biased attention compiled for key heads of `d` and value heads of `e` elements (at first use)."""
+    if (d, e) not in _biased_mma_libs:
+        if not torch.cuda.is_available():
+            raise BackendError("no CUDA device: the engine has no CPU path")
+        lib = specialised_kernel_library("attention_biased_mma.cu", {"MRS_HEAD_DIM": d, "MRS_VALUE_DIM": e})
+        lib.mrs_attention_biased_mma.argtypes = [_c_int] + [_c_vp] * 5 + [_c_int, _c_vp, _c_int, _c_vp, _c_vp, _c_int, _c_vp, _c_int,
+                                                 _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_int, _c_vp]
+        lib.mrs_attention_biased_mma.restype = _c_int
+        _biased_mma_libs[(d, e)] = lib
+    return _biased_mma_libs[(d, e)]
+
+
+def attention_biased_mma(q, k_cache, v_cache, positions, block_table, tiles, out, nq: int, nkv: int, d: int, e: int, scale: float,
+                         cap: float = 0.0, window: int = 0, keep_first: int = 0, bias: torch.Tensor | None = None,
+                         gate: torch.Tensor | None = None, sink: bool = False, narrow: bool = False) -> None:
+    """`attention_biased_simt`'s formulas on the tensor cores, bfloat16, over a list of tiles (sequence, first row, tokens, 0):
+    `narrow` tiles hold up to 16 // (nq // nkv) tokens (decoded tokens, short portions), the others up to 64 // (nq // nkv)."""
+    tokens = q.shape[0]
+    _need(q, torch.bfloat16, "q", (tokens, nq * d))
+    _need(k_cache, torch.bfloat16, "key pages")
+    _need(v_cache, torch.bfloat16, "value pages")
+    _need(out, torch.bfloat16, "attention out", (tokens, nq * e))
+    _need(positions, torch.int32, "positions", (tokens,))
+    _need(block_table, torch.int32, "block_table")
+    _need(tiles, torch.int32, "tiles")
+    page_size = k_cache.shape[2]
+    if tiles.dim() != 2 or tiles.shape[1] != 4:
+        raise InvalidRequest("attention tiles must be [n, 4] (sequence, first token, tokens, 0)")
+    if tuple(k_cache.shape[1:]) != (nkv, page_size, d) or tuple(v_cache.shape[1:]) != (nkv, page_size, e):
+        raise InvalidRequest("attention: the pages do not match heads and head sizes")
+    if bias is not None:
+        _need(bias, torch.float32, "distance bias")
+        if bias.dim() != 2 or bias.shape[1] != nq:
+            raise InvalidRequest("attention: the distance bias must be [rows, query heads]")
+    if gate is not None:
+        _need(gate, torch.float32, "attention gate", (tokens, nq))
+    lib = attention_biased_mma_library(d, e)
+    _check(lib.mrs_attention_biased_mma(int(narrow), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), positions.data_ptr(),
+                                        block_table.data_ptr(), block_table.shape[1], tiles.data_ptr(), tiles.shape[0], out.data_ptr(),
+                                        _ptr(bias), bias.shape[0] if bias is not None else 0, _ptr(gate), nq, nkv, page_size,
+                                        float(scale), float(cap), int(window), int(keep_first), int(sink), _stream()),
+           "attention_biased_mma")

@@ -22,7 +22,8 @@ import torch
 from .. import kernels
 from ..errors import InvalidRequest
 from ..weights.spec import WeightSpec
-from .base import MIXERS, KVNeed, Mixer
+from .attention import attention_tile_lists, plan_attention_tiles
+from .base import MIXERS, KVNeed, Mixer, StepFacts
 from .linear import linear
 
 
@@ -81,6 +82,7 @@ class BiasedWindowAttention(Mixer):
         self.leaf.update(names or {})
         self.fused = self.o = self.bias = self.distance_bias = None
         self.mix = 0.0
+        self._plan_arguments = None
 
     def _check_bias_table(self, rows: int) -> None:
         if rows < 2 or self.bias_far <= rows // 2:
@@ -147,7 +149,36 @@ class BiasedWindowAttention(Mixer):
                                ctx.slots[cache.group] if write_cache else None, self.nq, self.nkv, self.d, self.e,
                                v_first=v_first, mix_mode=mode, mix=self.mix, gate_out=gate)
         out = torch.empty((tokens, self.nq * self.e), dtype=dtype, device=device)
-        kernels.attention_biased_simt(q, cache.k, cache.v, ctx.positions, ctx.seq_of_token, ctx.block_tables[cache.group], out,
-                                      self.nq, self.nkv, self.d, self.e, self.scale, self.softcap, self.window, self.keep_first,
-                                      self.distance_bias, gate, self.sink)
+        table = ctx.block_tables[cache.group]
+        arguments = self._tile_plan()
+        if not arguments:
+            # the 32-bit path and head sizes that the tensor-core kernel does not take: one warp a (token, head)
+            kernels.attention_biased_simt(q, cache.k, cache.v, ctx.positions, ctx.seq_of_token, table, out, self.nq, self.nkv,
+                                          self.d, self.e, self.scale, self.softcap, self.window, self.keep_first,
+                                          self.distance_bias, gate, self.sink)
+        else:
+            # decoded tokens and short portions in tiles of 16 rows whose warps share the keys, longer portions in tiles of 64
+            narrow, wide, _, _ = plan_attention_tiles(ctx, *arguments)
+            for tiles, is_narrow in ((narrow, True), (wide, False)):
+                if tiles is not None:
+                    kernels.attention_biased_mma(q, cache.k, cache.v, ctx.positions, table, tiles, out, self.nq, self.nkv, self.d,
+                                                 self.e, self.scale, self.softcap, self.window, self.keep_first, self.distance_bias,
+                                                 gate, self.sink, narrow=is_narrow)
         return linear(out, self.o, out_dtype=torch.float32)
+
+    def _tile_plan(self) -> tuple:
+        """What the tile planner is asked for this attention ((): no tiles, the CUDA-core kernel takes every row)."""
+        if self._plan_arguments is None:
+            group = self.nq // self.nkv
+            if self.runtime.dtype is torch.bfloat16 and \
+                    kernels.attention_biased_mma_supported(self.d, self.e, group, self.runtime.page_size):
+                # the window enters the plan only as the reach of a tile's keys; kept first tokens add a block at most
+                self._plan_arguments = (group, kernels.MMA_ROWS_WIDE, self.nkv, self.window, 128, kernels.sm_count(self.o.device))
+            else:
+                self._plan_arguments = ()
+        return self._plan_arguments
+
+    def step_signature(self, facts: StepFacts):
+        """The lengths of a step's two tile lists (None: no list is planned)."""
+        arguments = self._tile_plan()
+        return attention_tile_lists(facts, *arguments).signature() if arguments else None

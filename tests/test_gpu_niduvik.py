@@ -201,8 +201,9 @@ def test_distance_buckets_are_the_plain_ones():
             assert table[min(n, len(table) - 1)] == P.distance_bucket(n, rows, far), (rows, far, n)
 
 
-def run_attention(dtype, T_, H, G, d, e, size, keep, rows, far, cap, scale, page, q, k, v, rel, gate, seed):
-    """The two attention kernels on one sequence whose pages lie scattered in a larger pool."""
+def run_attention(dtype, T_, H, G, d, e, size, keep, rows, far, cap, scale, page, q, k, v, rel, gate, seed, kernel="simt"):
+    """The attention kernels on one sequence whose pages lie scattered in a larger pool: `kernel` "simt" (one warp a row),
+    "rows" or "keys" (the tensor-core kernel over tiles of 64 or of 16 rows)."""
     from mini_rsglang_b200 import kernels
     from mini_rsglang_b200.parts.attention_biased import distance_buckets
 
@@ -220,8 +221,15 @@ def run_attention(dtype, T_, H, G, d, e, size, keep, rows, far, cap, scale, page
     bias = rel.float()[torch.tensor(distance_buckets(rows, far))].to(DEV).contiguous()
     out = torch.empty(T_, H * e, dtype=dtype, device=DEV)
     positions = torch.arange(T_, dtype=torch.int32, device=DEV)
-    kernels.attention_biased_simt(q_out, k_cache, v_cache, positions, torch.zeros(T_, dtype=torch.int32, device=DEV),
-                                  table.view(1, -1).to(DEV), out, H, G, d, e, scale, cap, size, keep, bias, gate_out, True)
+    if kernel == "simt":
+        kernels.attention_biased_simt(q_out, k_cache, v_cache, positions, torch.zeros(T_, dtype=torch.int32, device=DEV),
+                                      table.view(1, -1).to(DEV), out, H, G, d, e, scale, cap, size, keep, bias, gate_out, True)
+    else:
+        per = (64 if kernel == "rows" else 16) // (H // G)
+        tiles = torch.tensor([[0, first, min(per, T_ - first), 0] for first in range(0, T_, per)] + [[0, 0, 0, 0]],
+                             dtype=torch.int32, device=DEV)                  # and an entry without tokens, as padded lists have
+        kernels.attention_biased_mma(q_out, k_cache, v_cache, positions, table.view(1, -1).to(DEV), tiles, out, H, G, d, e, scale,
+                                     cap, size, keep, bias, gate_out, True, narrow=kernel == "keys")
     return out.double().cpu().view(T_, H, e)
 
 
@@ -251,16 +259,38 @@ def test_attention_kernel_random(H, G, d, e, size, keep, rows, far, page):
     assert (got16 - want16).abs().max() < 0.02 * max(1.0, want16.abs().max().item())
 
 
-@pytest.mark.parametrize("size,keep,page", [(20, 3, 4), (64, 6, 16), (17, 0, 8), (33, 40, 16)])
-def test_attention_kernel_sees_exactly_its_window_and_first_tokens(size, keep, page):
+@pytest.mark.parametrize("kernel", ["rows", "keys"])
+@pytest.mark.parametrize("H,G,d,e,size,keep,rows,far,page", [
+    (4, 2, 32, 48, 20, 3, 12, 50.0, 4), (3, 3, 96, 32, 9, 1, 7, 30.0, 16), (2, 1, 16, 16, 1000, 0, 4, 9.0, 8),
+    (8, 2, 128, 128, 64, 5, 16, 100.0, 16), (2, 2, 256, 256, 33, 40, 6, 20.0, 16), (20, 1, 16, 32, 70, 3, 8, 40.0, 16),
+    (1, 1, 48, 16, 1, 0, 32, 200.0, 4)])
+def test_tensor_core_attention_kernel_random(kernel, H, G, d, e, size, keep, rows, far, page):
+    if kernel == "keys" and H // G > 16:
+        pytest.skip("tiles of 16 rows hold groups of up to 16 query heads")
+    T_ = 200
+    torch.manual_seed(H * 100 + d)
+    q, k, v = torch.randn(T_, H, d), torch.randn(T_, G, d), torch.randn(T_, G, e)
+    rel, gate = torch.randn(rows, H).double(), torch.randn(T_, H).double()
+    scale, cap = 0.7 / d ** 0.5, 5.0
+    q16, k16, v16 = (x.bfloat16().double() for x in (q, k, v))
+    want = plain_attention(q16, k16, v16, rel, gate, scale, cap, far, size, keep)
+    got = run_attention(torch.bfloat16, T_, H, G, d, e, size, keep, rows, far, cap, scale, page, q, k, v, rel, gate, 4, kernel)
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max() < 0.02 * max(1.0, want.abs().max().item())
+
+
+@pytest.mark.parametrize("kernel", ["simt", "rows", "keys"])
+@pytest.mark.parametrize("size,keep,page", [(20, 3, 4), (64, 6, 16), (17, 0, 8), (33, 40, 16), (100, 70, 16)])
+def test_attention_kernel_sees_exactly_its_window_and_first_tokens(kernel, size, keep, page):
     """A query whose one key stands out (its score hits the cap, the others lie far below): the key just inside the
     window, just outside it, the last kept first token, the first token that is not kept, a far kept token, keys at page
     borders.  With a wrong edge the output is another token's value."""
-    T_, H, G, d, e, rows, far = 210, 2, 1, 16, 8, 8, 40.0
+    T_, H, G, d, e, rows, far = 210, 2, 1, 16, 16, 8, 40.0
     torch.manual_seed(size)
     i = T_ - 1
-    targets = sorted({i - size + 1, i - size, max(keep - 1, 0), keep, 0, i, (i - size + 1) // page * page, (i // page) * page - 1} &
-                     set(range(T_)))
+    dtype, tol = (torch.float32, 1e-5) if kernel == "simt" else (torch.bfloat16, 0.03)
+    targets = sorted({i - size + 1, i - size, max(keep - 1, 0), keep, 0, i, (i - size + 1) // page * page, (i // page) * page - 1,
+                      63, 64, 127, 128} & set(range(T_)))
     for target in targets:
         q, k = 0.01 * torch.randn(T_, H, d).double(), 0.01 * torch.randn(T_, G, d).double()
         v = torch.randn(T_, G, e).double()
@@ -268,13 +298,15 @@ def test_attention_kernel_sees_exactly_its_window_and_first_tokens(size, keep, p
         direction /= direction.norm()
         q[i] = 30.0 * direction
         k[target, 0] = 30.0 * direction
+        if dtype is torch.bfloat16:
+            q, k, v = (x.bfloat16().double() for x in (q, k, v))
         rel, gate = 0.1 * torch.randn(rows, H).double(), torch.randn(T_, H).double()
         want = plain_attention(q, k, v, rel, gate, 1.0, 12.0, far, size, keep)
-        got = run_attention(torch.float32, T_, H, G, d, e, size, keep, rows, far, 12.0, 1.0, page, q, k, v, rel, gate, target)
+        got = run_attention(dtype, T_, H, G, d, e, size, keep, rows, far, 12.0, 1.0, page, q, k, v, rel, gate, target, kernel)
         seen = P.visible(i, target, size, keep)
         alone = (want[i, 0] / torch.sigmoid(gate[i, 0]) - v[target, 0]).abs().max()
         assert (alone < 1e-2) == seen, f"target {target}: the plain implementation itself does not single the key out"
-        assert (got - want).abs().max() < 1e-5, f"key {target} (seen: {seen}) with window {size}, kept {keep}"
+        assert (got - want).abs().max() < tol, f"key {target} (seen: {seen}) with window {size}, kept {keep}"
 
 
 def recurrence_inputs(T_, heads, P_, N, G, taps, seed):
@@ -289,10 +321,11 @@ def recurrence_inputs(T_, heads, P_, N, G, taps, seed):
 
 @pytest.mark.parametrize("heads,P_,N,G,taps,parts", [(3, 20, 24, 1, 4, 3), (4, 16, 8, 4, 2, 1), (2, 24, 40, 2, 1, 1), (1, 64, 130, 1, 3, 4),
                                                      (8, 64, 128, 2, 4, 2)])
-def test_recurrence_kernels_in_portions_with_slots_used_again(heads, P_, N, G, taps, parts):
+@pytest.mark.parametrize("chunk", [0, 16])
+def test_recurrence_kernels_in_portions_with_slots_used_again(heads, P_, N, G, taps, parts, chunk):
     """Convolution, recurrence and the gated norm in parts against the plain functions: two sequences side by side, cut
     into portions of 1 to 40 tokens (also shorter than the convolution), in state slots that held another sequence's
-    state before."""
+    state before; the recurrence in one go (chunk 0) and in chunks of 16 rows that run side by side."""
     from mini_rsglang_b200 import kernels
 
     lengths, cuts = [97, 61], [[40, 1, 2, 1, 1, 33, 19], [1, 1, 3, 56]]
@@ -333,7 +366,7 @@ def test_recurrence_kernels_in_portions_with_slots_used_again(heads, P_, N, G, t
         kernels.causal_conv_silu(rows, inner, dev["conv"], dev["conv_b"], conv_state, positions, seq_of, q_start, slot_of, xbc)
         y = torch.zeros(rows.shape[0], inner, device=DEV)
         kernels.ssm_scan(xbc, rows[:, inner + channels:], dev["dt_bias"], dev["a_log"], dev["d"], ssm_state, positions, q_start,
-                         slot_of, y, heads, G, N, P_)
+                         slot_of, y, heads, G, N, P_, chunk_len=chunk)
         out = torch.empty(rows.shape[0], inner, device=DEV)
         kernels.gated_part_norm(y, rows[:, :inner], dev["norm"], 1e-5, out, parts)
         for b, (s, n) in enumerate(batch):
