@@ -250,7 +250,7 @@ def hybrid_run(args, torch, peak: dict) -> dict:
         config = config_from_dict(raw)
         page = 16
         pages = batch * (-(-context // page)) + 2 * (-(-prompt_len // page)) + 8
-        limits = RuntimeConfig(max_seq_len=max(context, prompt_len), page_size=page, prefill_budget=prompt_len, max_running=max(batch, 2))
+        limits = RuntimeConfig(max_seq_len=max(context, prompt_len), page_size=page, prefill_budget=prompt_len, max_running=batch + 1)
         engine = EngineHandle.from_random(config, seed=1, dtype="bfloat16", config=limits, num_pages=pages)
         runner = engine.runner
         for entry in runner.storage.entries:
