@@ -100,7 +100,6 @@ MRS_EXPORT int mrs_causal_conv_silu(const float* in, int in_stride, int offset, 
 // of S and the rows n = s * per + i of it in registers (lanes of one p are neighbours, so that y's sum over n is a few shuffles).
 // xbc [tokens, heads * P + 2 * groups * N] float32 (x | B | C after convolution and silu), raw dt a column range of
 // the projection's rows, y [tokens, heads * P] float32.  ssm_state [slots, heads, N, P].
-// The loads of the next token are issued before the arithmetic of this one.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.0f) + log1pf(expf(-fabsf(x))); }
 
@@ -111,6 +110,13 @@ __device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.0f) + l
 // chunk again from that state and writes y.
 enum { SSM_WHOLE = 0, SSM_LOCAL = 1, SSM_FINAL = 2 };
 
+// Rows are taken SSM_BATCH at a time (fewer where the state is large): the block first brings their B, C, x and the
+// step sizes and decays (softplus and exponentials once a row, not once a warp) into shared memory with coalesced loads,
+// then every thread walks them.  In shared memory a row's B (and C) lie as [i / 4][s][i % 4] for the element n = s * per + i,
+// padded with zeros to 16 elements a lane: a thread reads its 16 values as four vectors, and the lanes of a warp read
+// neighbouring vectors.
+#define SSM_BATCH 32
+
 template <int MODE>
 __global__ void ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt_in, int dt_stride,
                                 const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
@@ -118,9 +124,10 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, const float* __re
                                 const int* __restrict__ q_start, const int* __restrict__ state_slots, float* __restrict__ y,
                                 int heads, int groups, int N, int P, int lanes_per_column, int per, int write_state,
                                 float* __restrict__ chunk_state, float* __restrict__ chunk_decay, int chunk_len, int max_chunks,
-                                int slices, int columns) {
+                                int slices, int columns, int batch) {
     pdl_launch_dependents();
     pdl_wait();
+    extern __shared__ __align__(16) float ssm_smem[];
     const int seq = blockIdx.x, head = blockIdx.y / slices, slice = blockIdx.y % slices, chunk = blockIdx.z;
     const int seq_start = q_start[seq], seq_end = q_start[seq + 1];
     const int slot = state_slots[seq];
@@ -128,11 +135,20 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, const float* __re
     const int start_row = MODE == SSM_WHOLE ? seq_start : seq_start + chunk * chunk_len;
     const int end_row = MODE == SSM_WHOLE ? seq_end : min(seq_end, start_row + chunk_len);
     if (start_row >= end_row) return;
-    const int s = threadIdx.x % lanes_per_column, p = slice * columns + threadIdx.x / lanes_per_column;
-    const bool live = p < P && (int)threadIdx.x / lanes_per_column < columns;
+    const int s = threadIdx.x % lanes_per_column, column = threadIdx.x / lanes_per_column, p = slice * columns + column;
+    const bool live = p < P && column < columns;
     const int group = head / (heads / groups);
     const int inner = heads * P, row_width = inner + 2 * groups * N;
     const int n0 = s * per;
+    const int padded = SSM_PER_LANE * lanes_per_column;              // floats of a row's B (or C) in shared memory
+    float* b_rows = ssm_smem;                                        // [batch][padded]
+    float* c_rows = b_rows + (size_t)batch * padded;                 // [batch][padded]
+    float* x_rows = c_rows + (size_t)batch * padded;                 // [batch][columns]
+    float* dt_rows = x_rows + (size_t)batch * columns;               // [batch] step sizes
+    float* decay_rows = dt_rows + batch;                             // [batch] decays
+    const int used = min(batch, end_row - start_row) * padded;       // the padding of the rows in use stays zero
+    for (int i = threadIdx.x; i < used; i += blockDim.x) b_rows[i] = 0.0f, c_rows[i] = 0.0f;
+
     float* state = MODE == SSM_WHOLE ? ssm_state + (long long)slot * state_stride + (size_t)head * N * P
                                      : chunk_state + (((size_t)seq * heads + head) * max_chunks + chunk) * N * P;
     float S[SSM_PER_LANE];
@@ -143,39 +159,48 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, const float* __re
     const float bias = dt_bias[head], rate = -expf(a_log[head]), skip = d_skip[head];
     float decays = 1.0f;
 
-    float b_next[SSM_PER_LANE], c_next[SSM_PER_LANE], x_next = 0.0f, dt_next = 0.0f;
-    auto load = [&](int row) {
-        const float* r = xbc + (size_t)row * row_width;
-        x_next = live ? r[head * P + p] : 0.0f;
-        dt_next = dt_in[(size_t)row * dt_stride + head];
-#pragma unroll
-        for (int i = 0; i < SSM_PER_LANE; ++i) {
-            const bool in = i < per && n0 + i < N;
-            b_next[i] = in ? r[inner + group * N + n0 + i] : 0.0f;
-            if (MODE != SSM_LOCAL) c_next[i] = in ? r[inner + groups * N + group * N + n0 + i] : 0.0f;
+    for (int first = start_row; first < end_row; first += batch) {
+        const int count = min(batch, end_row - first);
+        __syncthreads();                                             // the rows before are read, the zeros are written
+        for (int i = threadIdx.x; i < count * N; i += blockDim.x) {
+            const int t = i / N, n = i % N;
+            const float* r = xbc + (size_t)(first + t) * row_width + inner + group * N + n;
+            const int lane_of = n / per, at = n % per;
+            const int where = t * padded + (((at >> 2) * lanes_per_column + lane_of) << 2) + (at & 3);
+            b_rows[where] = r[0];
+            if (MODE != SSM_LOCAL) c_rows[where] = r[groups * N];
         }
-    };
-    load(start_row);
-    for (int row = start_row; row < end_row; ++row) {
-        float b[SSM_PER_LANE], c[SSM_PER_LANE];
-        const float x = x_next, dt = softplus_f(dt_next + bias);
-#pragma unroll
-        for (int i = 0; i < SSM_PER_LANE; ++i) {
-            b[i] = b_next[i];
-            if (MODE != SSM_LOCAL) c[i] = c_next[i];
+        for (int i = threadIdx.x; i < count * columns; i += blockDim.x) {
+            const int t = i / columns, c = i % columns;
+            x_rows[i] = slice * columns + c < P ? xbc[(size_t)(first + t) * row_width + head * P + slice * columns + c] : 0.0f;
         }
-        if (row + 1 < end_row) load(row + 1);
-        const float decay = expf(rate * dt), dx = dt * x;
-        if (MODE == SSM_LOCAL) decays *= decay;
-        float sum = 0.0f;
-#pragma unroll
-        for (int i = 0; i < SSM_PER_LANE; ++i) {
-            S[i] = decay * S[i] + dx * b[i];
-            if (MODE != SSM_LOCAL) sum += S[i] * c[i];
+        if (threadIdx.x < count) {
+            const float dt = softplus_f(dt_in[(size_t)(first + threadIdx.x) * dt_stride + head] + bias);
+            dt_rows[threadIdx.x] = dt;
+            decay_rows[threadIdx.x] = expf(rate * dt);
         }
-        if (MODE != SSM_LOCAL) {
-            for (int o = 1; o < lanes_per_column; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            if (live && s == 0) y[(size_t)row * inner + head * P + p] = sum + skip * x;
+        __syncthreads();
+        for (int t = 0; t < count; ++t) {
+            const float x = column < columns ? x_rows[t * columns + column] : 0.0f;
+            const float decay = decay_rows[t], dx = dt_rows[t] * x;
+            if (MODE == SSM_LOCAL) decays *= decay;
+            float sum = 0.0f;
+#pragma unroll
+            for (int v = 0; v < SSM_PER_LANE / 4; ++v) {
+                const float4 b = *reinterpret_cast<const float4*>(b_rows + t * padded + ((v * lanes_per_column + s) << 2));
+                S[4 * v + 0] = decay * S[4 * v + 0] + dx * b.x;
+                S[4 * v + 1] = decay * S[4 * v + 1] + dx * b.y;
+                S[4 * v + 2] = decay * S[4 * v + 2] + dx * b.z;
+                S[4 * v + 3] = decay * S[4 * v + 3] + dx * b.w;
+                if (MODE != SSM_LOCAL) {
+                    const float4 c = *reinterpret_cast<const float4*>(c_rows + t * padded + ((v * lanes_per_column + s) << 2));
+                    sum += S[4 * v + 0] * c.x + S[4 * v + 1] * c.y + S[4 * v + 2] * c.z + S[4 * v + 3] * c.w;
+                }
+            }
+            if (MODE != SSM_LOCAL) {
+                for (int o = 1; o < lanes_per_column; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                if (live && s == 0) y[(size_t)(first + t) * inner + head * P + p] = sum + skip * x;
+            }
         }
     }
     if (MODE == SSM_LOCAL && threadIdx.x == 0 && slice == 0) chunk_decay[((size_t)seq * heads + head) * max_chunks + chunk] = decays;
@@ -233,26 +258,33 @@ MRS_EXPORT int mrs_ssm_scan(const float* xbc, const float* dt_in, int dt_stride,
     const int slices = (P + columns - 1) / columns;
     const int threads = (columns * lanes + 31) / 32 * 32;
     if ((long long)heads * slices > 65535) return MRS_BAD_ARGUMENT;
+    // rows a batch: what 40 KB of shared memory hold (several blocks share an SM), at least one, at most as many as threads
+    const int row_floats = 2 * SSM_PER_LANE * lanes + columns + 2;
+    int batch = (40 * 1024 / 4) / row_floats;
+    if (batch > SSM_BATCH) batch = SSM_BATCH;
+    if (batch > threads) batch = threads;
+    if (batch < 1) batch = 1;
+    const size_t smem = (size_t)batch * row_floats * sizeof(float);
     if (chunk_len == 0) {
-        MRS_LAUNCH(ssm_scan_kernel<SSM_WHOLE>, dim3(sequences, heads * slices), threads, 0, stream, xbc, dt_in, dt_stride, dt_bias, a_log, d_skip,
+        MRS_LAUNCH(ssm_scan_kernel<SSM_WHOLE>, dim3(sequences, heads * slices), threads, smem, stream, xbc, dt_in, dt_stride, dt_bias, a_log, d_skip,
                    ssm_state, state_stride, positions, q_start, state_slots, y, heads, groups, N, P, lanes, per, write_state,
-                   (float*)nullptr, (float*)nullptr, 0, 0, slices, columns);
+                   (float*)nullptr, (float*)nullptr, 0, 0, slices, columns, batch);
         MRS_RETURN_LAUNCH_STATUS();
     }
     const int max_chunks = (tokens + chunk_len - 1) / chunk_len;
     if (max_chunks > 65535) return MRS_BAD_ARGUMENT;
     float* chunk_state = scratch;
     float* chunk_decay = scratch + (size_t)sequences * heads * max_chunks * N * P;
-    MRS_LAUNCH(ssm_scan_kernel<SSM_LOCAL>, dim3(sequences, heads * slices, max_chunks), threads, 0, stream, xbc, dt_in, dt_stride, dt_bias, a_log,
+    MRS_LAUNCH(ssm_scan_kernel<SSM_LOCAL>, dim3(sequences, heads * slices, max_chunks), threads, smem, stream, xbc, dt_in, dt_stride, dt_bias, a_log,
                d_skip, ssm_state, state_stride, positions, q_start, state_slots, y, heads, groups, N, P, lanes, per, write_state,
-               chunk_state, chunk_decay, chunk_len, max_chunks, slices, columns);
+               chunk_state, chunk_decay, chunk_len, max_chunks, slices, columns, batch);
     const int elements = N * P;
     int element_blocks = (elements + 255) / 256;
     if (element_blocks > 64) element_blocks = 64;
     MRS_LAUNCH(ssm_chunk_states_kernel, dim3(sequences, heads, element_blocks), 256, 0, stream, ssm_state, state_stride, positions, q_start,
                state_slots, chunk_state, (const float*)chunk_decay, heads, elements, chunk_len, max_chunks, write_state);
-    MRS_LAUNCH(ssm_scan_kernel<SSM_FINAL>, dim3(sequences, heads * slices, max_chunks), threads, 0, stream, xbc, dt_in, dt_stride, dt_bias, a_log,
+    MRS_LAUNCH(ssm_scan_kernel<SSM_FINAL>, dim3(sequences, heads * slices, max_chunks), threads, smem, stream, xbc, dt_in, dt_stride, dt_bias, a_log,
                d_skip, ssm_state, state_stride, positions, q_start, state_slots, y, heads, groups, N, P, lanes, per, write_state,
-               chunk_state, chunk_decay, chunk_len, max_chunks, slices, columns);
+               chunk_state, chunk_decay, chunk_len, max_chunks, slices, columns, batch);
     MRS_RETURN_LAUNCH_STATUS();
 }

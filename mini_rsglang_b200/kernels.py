@@ -1214,14 +1214,14 @@ def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dt_bias, a_log, d_skip, ssm_st
 def ssm_chunk_length(tokens: int, sequences: int, heads: int, n_state: int, head_dim: int, sms: int) -> int:
     """Rows of a chunk of the recurrence, 0 for none, from a step's shapes alone (a recorded step keeps its choice): chunks
     pay twice the arithmetic for blocks that run side by side, so they are taken where the sequences' own blocks (one a
-    head and slice of 128 threads, four to an SM) fill less than half of the GPU and the portions are long."""
+    head and slice of 128 threads, four to an SM) fill less than a quarter of the GPU and the portions are long."""
     lanes = 1
     while lanes < 32 and -(-n_state // lanes) > 16:
         lanes *= 2
     slices = -(-head_dim // max(1, min(128 // lanes, head_dim)))
     blocks = sequences * heads * slices
     room = 4 * sms
-    if tokens < 512 or tokens < 128 * sequences or 2 * blocks > room:
+    if tokens < 512 or tokens < 128 * sequences or 4 * blocks > room:
         return 0
     chunks = min(room // blocks, tokens // 64)
     if chunks < 2:
