@@ -293,7 +293,7 @@ __global__ void __launch_bounds__(THREADS) attention_biased_rows_kernel(
 __global__ void __launch_bounds__(THREADS) attention_biased_keys_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, const int* __restrict__ positions,
     const int* __restrict__ block_table, int table_width, const Tile* __restrict__ tiles, bf16* __restrict__ out, int nq, int nkv,
-    int page_size, int page_shift, Extras x) {
+    int page_size, int page_shift, Extras x, float* __restrict__ part_o, float* __restrict__ part_ml, int splits) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -312,6 +312,9 @@ __global__ void __launch_bounds__(THREADS) attention_biased_keys_kernel(
     const int first_pos = positions[tile.first_token], last_pos = positions[tile.first_token + tile.tokens - 1];
     const int key_end = last_pos + 1;
     const Blocks blocks = blocks_of(first_pos, key_end, KV_NARROW, x);
+    // with `splits` CTAs a tile the blocks are dealt in runs; the partial results meet in `attention_biased_combine_kernel`
+    const int split = blockIdx.z, share = (blocks.count + splits - 1) / splits;
+    const int block_first = min(blocks.count, split * share), block_last = min(blocks.count, block_first + share);
 
     int row_pos[2], row_head[2];
 #pragma unroll
@@ -327,14 +330,14 @@ __global__ void __launch_bounds__(THREADS) attention_biased_keys_kernel(
         for (int e = 0; e < 4; ++e) o[dt][e] = 0.0f;
     float row_max[2] = {-CUDART_INF_F, -CUDART_INF_F}, row_sum[2] = {0.0f, 0.0f};
 
-    if (blocks.count > 0) {
-        load_kv_block<KV_NARROW, D>(k_tiles, k_cache, pages, blocks.at(0) * KV_NARROW, key_end, kv_head, nkv, page_size, page_shift);
-        load_kv_block<KV_NARROW, E>(v_tiles, v_cache, pages, blocks.at(0) * KV_NARROW, key_end, kv_head, nkv, page_size, page_shift);
+    if (block_first < block_last) {
+        load_kv_block<KV_NARROW, D>(k_tiles, k_cache, pages, blocks.at(block_first) * KV_NARROW, key_end, kv_head, nkv, page_size, page_shift);
+        load_kv_block<KV_NARROW, E>(v_tiles, v_cache, pages, blocks.at(block_first) * KV_NARROW, key_end, kv_head, nkv, page_size, page_shift);
     }
     cp_async_commit();
-    for (int i = 0; i < blocks.count; ++i) {
-        const int stage = i & 1;
-        if (i + 1 < blocks.count) {
+    for (int i = block_first; i < block_last; ++i) {
+        const int stage = (i - block_first) & 1;
+        if (i + 1 < block_last) {
             load_kv_block<KV_NARROW, D>(k_tiles + (stage ^ 1) * KV_NARROW * D, k_cache, pages, blocks.at(i + 1) * KV_NARROW, key_end, kv_head, nkv, page_size, page_shift);
             load_kv_block<KV_NARROW, E>(v_tiles + (stage ^ 1) * KV_NARROW * E, v_cache, pages, blocks.at(i + 1) * KV_NARROW, key_end, kv_head, nkv, page_size, page_shift);
         }
@@ -381,19 +384,53 @@ __global__ void __launch_bounds__(THREADS) attention_biased_keys_kernel(
     for (int idx = threadIdx.x; idx < ROWS_NARROW * E; idx += THREADS) {
         const int row = idx / E, col = idx % E;
         if (row >= rows) continue;
-        float m = x.sink ? 0.0f : -CUDART_INF_F;
+        const bool with_sink = x.sink && splits == 1;          // among several CTAs the sink joins in the combine kernel
+        float m = with_sink ? 0.0f : -CUDART_INF_F;
 #pragma unroll
         for (int w = 0; w < 4; ++w) m = fmaxf(m, merge_ml[(w * ROWS_NARROW + row) * 2]);
         const float base = m == -CUDART_INF_F ? 0.0f : m;
-        float sum = x.sink ? exp2f(-base) : 0.0f, acc = 0.0f;
+        float sum = with_sink ? exp2f(-base) : 0.0f, acc = 0.0f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
             const float f = exp2f(merge_ml[(w * ROWS_NARROW + row) * 2] - base);
             sum += merge_ml[(w * ROWS_NARROW + row) * 2 + 1] * f;
             acc += merge_o[(w * ROWS_NARROW + row) * E + col] * f;
         }
+        if (splits > 1) {
+            const size_t slot = (((size_t)blockIdx.x * nkv + kv_head) * splits + split) * ROWS_NARROW + row;
+            part_o[slot * E + col] = acc;
+            if (col == 0) part_ml[slot * 2] = m, part_ml[slot * 2 + 1] = sum;
+            continue;
+        }
         const int token = tile.first_token + row / group, head = kv_head * group + row % group;
         const float factor = (sum > 0.0f ? 1.0f / sum : 0.0f) * (x.gate ? x.gate[(size_t)token * nq + head] : 1.0f);
+        out[((size_t)token * nq + head) * E + col] = __float2bfloat16_rn(acc * factor);
+    }
+}
+
+// Merges the partial results of a tile's `splits` CTAs, adds the sink and applies the gate.
+__global__ void __launch_bounds__(THREADS) attention_biased_combine_kernel(
+    const float* __restrict__ part_o, const float* __restrict__ part_ml, const Tile* __restrict__ tiles, bf16* __restrict__ out,
+    const float* __restrict__ gate, int nq, int nkv, int splits, int sink) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const Tile tile = tiles[blockIdx.x];
+    const int kv_head = blockIdx.y, group = nq / nkv, rows = tile.tokens * group;
+    const size_t base_slot = ((size_t)blockIdx.x * nkv + kv_head) * splits * ROWS_NARROW;
+    for (int idx = threadIdx.x; idx < rows * E; idx += THREADS) {
+        const int row = idx / E, col = idx % E;
+        float m = sink ? 0.0f : -CUDART_INF_F;
+        for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(base_slot + (size_t)s * ROWS_NARROW + row) * 2]);
+        const float base = m == -CUDART_INF_F ? 0.0f : m;
+        float sum = sink ? exp2f(-base) : 0.0f, acc = 0.0f;
+        for (int s = 0; s < splits; ++s) {
+            const size_t slot = base_slot + (size_t)s * ROWS_NARROW + row;
+            const float f = exp2f(part_ml[slot * 2] - base);
+            sum += part_ml[slot * 2 + 1] * f;
+            acc += part_o[slot * E + col] * f;
+        }
+        const int token = tile.first_token + row / group, head = kv_head * group + row % group;
+        const float factor = (sum > 0.0f ? 1.0f / sum : 0.0f) * (gate ? gate[(size_t)token * nq + head] : 1.0f);
         out[((size_t)token * nq + head) * E + col] = __float2bfloat16_rn(acc * factor);
     }
 }
@@ -415,11 +452,18 @@ MRS_EXPORT int mrs_attention_biased_mma_key_dim() { return D; }
 MRS_EXPORT int mrs_attention_biased_mma_value_dim() { return E; }
 
 // narrow != 0: tiles of up to 16 / group tokens (keys mode); else tiles of up to 64 / group tokens (rows mode).
+// Scratch floats of `splits` > 1 CTAs a tile (tiles of 16 rows only).
+MRS_EXPORT long long mrs_attention_biased_mma_scratch_floats(int tiles, int nkv, int splits) {
+    return splits <= 1 ? 0 : (long long)tiles * nkv * splits * ROWS_NARROW * (E + 2);
+}
+
 MRS_EXPORT int mrs_attention_biased_mma(int narrow, const void* q, const void* k_cache, const void* v_cache, const int* positions,
                                         const int* block_table, int table_width, const int* tiles, int num_tiles, void* out,
                                         const float* bias, int bias_rows, const float* gate, int nq, int nkv, int page_size,
-                                        float scale, float cap, int window, int keep_first, int sink, void* stream) {
+                                        float scale, float cap, int window, int keep_first, int sink, int splits, float* scratch,
+                                        void* stream) {
     if (num_tiles <= 0) return 0;
+    if (splits < 1 || splits > 65535 || (splits > 1 && (!narrow || !scratch))) return MRS_BAD_ARGUMENT;
     const int shift = page_shift_of(page_size);
     if (shift < 0 || nkv <= 0 || nq % nkv || nq / nkv > (narrow ? ROWS_NARROW : ROWS_WIDE) || (bias && bias_rows <= 0) || window < 0 ||
         keep_first < 0)
@@ -435,10 +479,16 @@ MRS_EXPORT int mrs_attention_biased_mma(int narrow, const void* q, const void* k
         if (e != cudaSuccess) return (int)e;
         configured[narrow ? 1 : 0] = true;
     }
-    if (narrow)
-        MRS_LAUNCH(attention_biased_keys_kernel, dim3(num_tiles, nkv), THREADS, smem_keys, stream, (const bf16*)q, (const bf16*)k_cache,
-                   (const bf16*)v_cache, positions, block_table, table_width, (const Tile*)tiles, (bf16*)out, nq, nkv, page_size, shift, x);
-    else
+    if (narrow) {
+        float* part_o = scratch;
+        float* part_ml = scratch ? scratch + (size_t)num_tiles * nkv * splits * ROWS_NARROW * E : nullptr;
+        MRS_LAUNCH(attention_biased_keys_kernel, dim3(num_tiles, nkv, splits), THREADS, smem_keys, stream, (const bf16*)q,
+                   (const bf16*)k_cache, (const bf16*)v_cache, positions, block_table, table_width, (const Tile*)tiles, (bf16*)out, nq, nkv,
+                   page_size, shift, x, part_o, part_ml, splits);
+        if (splits > 1)
+            MRS_LAUNCH(attention_biased_combine_kernel, dim3(num_tiles, nkv), THREADS, 0, stream, (const float*)part_o,
+                       (const float*)part_ml, (const Tile*)tiles, (bf16*)out, gate, nq, nkv, splits, sink);
+    } else
         MRS_LAUNCH(attention_biased_rows_kernel, dim3(num_tiles, nkv), THREADS, smem_rows, stream, (const bf16*)q, (const bf16*)k_cache,
                    (const bf16*)v_cache, positions, block_table, table_width, (const Tile*)tiles, (bf16*)out, nq, nkv, page_size, shift, x);
     MRS_RETURN_LAUNCH_STATUS();

@@ -1246,17 +1246,21 @@ def attention_biased_mma_library(d: int, e: int) -> ctypes.CDLL:
             raise BackendError("no CUDA device: the engine has no CPU path")
         lib = specialised_kernel_library("attention_biased_mma.cu", {"MRS_HEAD_DIM": d, "MRS_VALUE_DIM": e})
         lib.mrs_attention_biased_mma.argtypes = [_c_int] + [_c_vp] * 5 + [_c_int, _c_vp, _c_int, _c_vp, _c_vp, _c_int, _c_vp, _c_int,
-                                                 _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_int, _c_vp]
+                                                 _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_int, _c_int, _c_vp, _c_vp]
         lib.mrs_attention_biased_mma.restype = _c_int
+        lib.mrs_attention_biased_mma_scratch_floats.argtypes = [_c_int, _c_int, _c_int]
+        lib.mrs_attention_biased_mma_scratch_floats.restype = ctypes.c_longlong
         _biased_mma_libs[(d, e)] = lib
     return _biased_mma_libs[(d, e)]
 
 
 def attention_biased_mma(q, k_cache, v_cache, positions, block_table, tiles, out, nq: int, nkv: int, d: int, e: int, scale: float,
                          cap: float = 0.0, window: int = 0, keep_first: int = 0, bias: torch.Tensor | None = None,
-                         gate: torch.Tensor | None = None, sink: bool = False, narrow: bool = False) -> None:
+                         gate: torch.Tensor | None = None, sink: bool = False, narrow: bool = False, splits: int = 1) -> None:
     """`attention_biased_simt`'s formulas on the tensor cores, bfloat16, over a list of tiles (sequence, first row, tokens, 0):
-    `narrow` tiles hold up to 16 // (nq // nkv) tokens (decoded tokens, short portions), the others up to 64 // (nq // nkv)."""
+    `narrow` tiles hold up to 16 // (nq // nkv) tokens (decoded tokens, short portions), the others up to 64 // (nq // nkv).
+    `splits` > 1 (narrow tiles): that many CTAs share a tile's key blocks and a second kernel merges them."""
+    global launch_count
     tokens = q.shape[0]
     _need(q, torch.bfloat16, "q", (tokens, nq * d))
     _need(k_cache, torch.bfloat16, "key pages")
@@ -1277,8 +1281,15 @@ def attention_biased_mma(q, k_cache, v_cache, positions, block_table, tiles, out
     if gate is not None:
         _need(gate, torch.float32, "attention gate", (tokens, nq))
     lib = attention_biased_mma_library(d, e)
+    scratch = None
+    if splits > 1:
+        if not narrow:
+            raise InvalidRequest("only tiles of 16 rows share their keys among CTAs")
+        scratch = attention_scratch(q.device, lib.mrs_attention_biased_mma_scratch_floats(tiles.shape[0], nkv, splits))
+        launch_count += 1
     _check(lib.mrs_attention_biased_mma(int(narrow), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), positions.data_ptr(),
                                         block_table.data_ptr(), block_table.shape[1], tiles.data_ptr(), tiles.shape[0], out.data_ptr(),
                                         _ptr(bias), bias.shape[0] if bias is not None else 0, _ptr(gate), nq, nkv, page_size,
-                                        float(scale), float(cap), int(window), int(keep_first), int(sink), _stream()),
+                                        float(scale), float(cap), int(window), int(keep_first), int(sink), int(splits), _ptr(scratch),
+                                        _stream()),
            "attention_biased_mma")

@@ -22,7 +22,7 @@ import torch
 from .. import kernels
 from ..errors import InvalidRequest
 from ..weights.spec import WeightSpec
-from .attention import attention_tile_lists, plan_attention_tiles
+from .attention import attention_tile_lists, choose_splits, plan_attention_tiles
 from .base import MIXERS, KVNeed, Mixer, StepFacts
 from .linear import linear
 
@@ -158,12 +158,16 @@ class BiasedWindowAttention(Mixer):
                                           self.distance_bias, gate, self.sink)
         else:
             # decoded tokens and short portions in tiles of 16 rows whose warps share the keys, longer portions in tiles of 64
-            narrow, wide, _, _ = plan_attention_tiles(ctx, *arguments)
+            narrow, wide, longest, _ = plan_attention_tiles(ctx, *arguments)
             for tiles, is_narrow in ((narrow, True), (wide, False)):
                 if tiles is not None:
+                    splits = 1
+                    if is_narrow:          # few rows: the keys in sight (the window and the kept tokens at most) are shared among CTAs
+                        reach = min(longest, self.window + self.keep_first) if self.window else longest
+                        splits = min(choose_splits(tiles.shape[0], self.nkv, reach, arguments[5]), 16)
                     kernels.attention_biased_mma(q, cache.k, cache.v, ctx.positions, table, tiles, out, self.nq, self.nkv, self.d,
                                                  self.e, self.scale, self.softcap, self.window, self.keep_first, self.distance_bias,
-                                                 gate, self.sink, narrow=is_narrow)
+                                                 gate, self.sink, narrow=is_narrow, splits=splits)
         return linear(out, self.o, out_dtype=torch.float32)
 
     def _tile_plan(self) -> tuple:

@@ -203,7 +203,7 @@ def test_distance_buckets_are_the_plain_ones():
 
 def run_attention(dtype, T_, H, G, d, e, size, keep, rows, far, cap, scale, page, q, k, v, rel, gate, seed, kernel="simt"):
     """The attention kernels on one sequence whose pages lie scattered in a larger pool: `kernel` "simt" (one warp a row),
-    "rows" or "keys" (the tensor-core kernel over tiles of 64 or of 16 rows)."""
+    "rows", "keys" or "split" (the tensor-core kernel over tiles of 64 rows, of 16 rows, of 16 rows with three CTAs a tile)."""
     from mini_rsglang_b200 import kernels
     from mini_rsglang_b200.parts.attention_biased import distance_buckets
 
@@ -225,11 +225,11 @@ def run_attention(dtype, T_, H, G, d, e, size, keep, rows, far, cap, scale, page
         kernels.attention_biased_simt(q_out, k_cache, v_cache, positions, torch.zeros(T_, dtype=torch.int32, device=DEV),
                                       table.view(1, -1).to(DEV), out, H, G, d, e, scale, cap, size, keep, bias, gate_out, True)
     else:
-        per = (64 if kernel == "rows" else 16) // (H // G)
+        per = (64 if kernel == "rows" else 16) // (H // G)          # "split": tiles of 16 rows whose key blocks three CTAs share
         tiles = torch.tensor([[0, first, min(per, T_ - first), 0] for first in range(0, T_, per)] + [[0, 0, 0, 0]],
                              dtype=torch.int32, device=DEV)                  # and an entry without tokens, as padded lists have
         kernels.attention_biased_mma(q_out, k_cache, v_cache, positions, table.view(1, -1).to(DEV), tiles, out, H, G, d, e, scale,
-                                     cap, size, keep, bias, gate_out, True, narrow=kernel == "keys")
+                                     cap, size, keep, bias, gate_out, True, narrow=kernel != "rows", splits=3 if kernel == "split" else 1)
     return out.double().cpu().view(T_, H, e)
 
 
@@ -259,13 +259,13 @@ def test_attention_kernel_random(H, G, d, e, size, keep, rows, far, page):
     assert (got16 - want16).abs().max() < 0.02 * max(1.0, want16.abs().max().item())
 
 
-@pytest.mark.parametrize("kernel", ["rows", "keys"])
+@pytest.mark.parametrize("kernel", ["rows", "keys", "split"])
 @pytest.mark.parametrize("H,G,d,e,size,keep,rows,far,page", [
     (4, 2, 32, 48, 20, 3, 12, 50.0, 4), (3, 3, 96, 32, 9, 1, 7, 30.0, 16), (2, 1, 16, 16, 1000, 0, 4, 9.0, 8),
     (8, 2, 128, 128, 64, 5, 16, 100.0, 16), (2, 2, 256, 256, 33, 40, 6, 20.0, 16), (20, 1, 16, 32, 70, 3, 8, 40.0, 16),
     (1, 1, 48, 16, 1, 0, 32, 200.0, 4)])
 def test_tensor_core_attention_kernel_random(kernel, H, G, d, e, size, keep, rows, far, page):
-    if kernel == "keys" and H // G > 16:
+    if kernel != "rows" and H // G > 16:
         pytest.skip("tiles of 16 rows hold groups of up to 16 query heads")
     T_ = 200
     torch.manual_seed(H * 100 + d)
@@ -279,7 +279,7 @@ def test_tensor_core_attention_kernel_random(kernel, H, G, d, e, size, keep, row
     assert (got - want).abs().max() < 0.02 * max(1.0, want.abs().max().item())
 
 
-@pytest.mark.parametrize("kernel", ["simt", "rows", "keys"])
+@pytest.mark.parametrize("kernel", ["simt", "rows", "keys", "split"])
 @pytest.mark.parametrize("size,keep,page", [(20, 3, 4), (64, 6, 16), (17, 0, 8), (33, 40, 16), (100, 70, 16)])
 def test_attention_kernel_sees_exactly_its_window_and_first_tokens(kernel, size, keep, page):
     """A query whose one key stands out (its score hits the cap, the others lie far below): the key just inside the
