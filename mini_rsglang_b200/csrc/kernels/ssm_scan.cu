@@ -110,12 +110,19 @@ __device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.0f) + l
 // chunk again from that state and writes y.
 enum { SSM_WHOLE = 0, SSM_LOCAL = 1, SSM_FINAL = 2 };
 
-// Rows are taken SSM_BATCH at a time (fewer where the state is large): the block first brings their B, C, x and the
-// step sizes and decays (softplus and exponentials once a row, not once a warp) into shared memory with coalesced loads,
-// then every thread walks them.  In shared memory a row's B (and C) lie as [i / 4][s][i % 4] for the element n = s * per + i,
+// Rows are taken SSM_BATCH at a time (fewer where the state is large): their B, C and x come into shared memory by
+// asynchronous copies, the step sizes and decays are computed once a row (not once a warp), and every thread walks them
+// while the next batch's copies are in flight.  In shared memory a row's B (and C) lie as [i / 4][s][i % 4] for the element n = s * per + i,
 // padded with zeros to 16 elements a lane: a thread reads its 16 values as four vectors, and the lanes of a warp read
 // neighbouring vectors.
-#define SSM_BATCH 32
+#define SSM_BATCH 16
+
+__device__ __forceinline__ void cp_async_f4(float* to, const float* from) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(to)), "l"(from));
+}
+__device__ __forceinline__ void cp_async_f1(float* to, const float* from) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(to)), "l"(from));
+}
 
 template <int MODE>
 __global__ void ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt_in, int dt_stride,
@@ -141,12 +148,13 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, const float* __re
     const int inner = heads * P, row_width = inner + 2 * groups * N;
     const int n0 = s * per;
     const int padded = SSM_PER_LANE * lanes_per_column;              // floats of a row's B (or C) in shared memory
-    float* b_rows = ssm_smem;                                        // [batch][padded]
-    float* c_rows = b_rows + (size_t)batch * padded;                 // [batch][padded]
-    float* x_rows = c_rows + (size_t)batch * padded;                 // [batch][columns]
-    float* dt_rows = x_rows + (size_t)batch * columns;               // [batch] step sizes
-    float* decay_rows = dt_rows + batch;                             // [batch] decays
-    const int used = min(batch, end_row - start_row) * padded;       // the padding of the rows in use stays zero
+    float* b_rows = ssm_smem;                                        // [2][batch][padded]
+    float* c_rows = b_rows + (size_t)2 * batch * padded;             // [2][batch][padded]
+    float* x_rows = c_rows + (size_t)2 * batch * padded;             // [2][batch][columns]
+    float* dt_rows = x_rows + (size_t)2 * batch * columns;           // [2][batch] step sizes
+    float* decay_rows = dt_rows + 2 * batch;                         // [2][batch] decays
+    const int rows_here = end_row - start_row;                       // the padding of the rows in use stays zero
+    const int used = (rows_here > batch ? 2 * batch : rows_here) * padded;
     for (int i = threadIdx.x; i < used; i += blockDim.x) b_rows[i] = 0.0f, c_rows[i] = 0.0f;
 
     float* state = MODE == SSM_WHOLE ? ssm_state + (long long)slot * state_stride + (size_t)head * N * P
@@ -159,41 +167,83 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, const float* __re
     const float bias = dt_bias[head], rate = -expf(a_log[head]), skip = d_skip[head];
     float decays = 1.0f;
 
-    for (int first = start_row; first < end_row; first += batch) {
-        const int count = min(batch, end_row - first);
-        __syncthreads();                                             // the rows before are read, the zeros are written
-        for (int i = threadIdx.x; i < count * N; i += blockDim.x) {
-            const int t = i / N, n = i % N;
-            const float* r = xbc + (size_t)(first + t) * row_width + inner + group * N + n;
-            const int lane_of = n / per, at = n % per;
-            const int where = t * padded + (((at >> 2) * lanes_per_column + lane_of) << 2) + (at & 3);
-            b_rows[where] = r[0];
-            if (MODE != SSM_LOCAL) c_rows[where] = r[groups * N];
+    // Two buffers: while the threads walk one batch of rows, the copies of the next are in flight (cp.async, 16 bytes
+    // where the sizes allow it), and the step sizes of the next batch wait in a register.
+    const bool vectors = per % 4 == 0 && N % 4 == 0 && row_width % 4 == 0 && (inner + group * N) % 4 == 0 && (groups * N) % 4 == 0 &&
+                         (reinterpret_cast<uintptr_t>(xbc) & 15) == 0;
+    auto fetch = [&](int buffer, int first, int count) {
+        float* b_to = b_rows + (size_t)buffer * batch * padded;
+        float* c_to = c_rows + (size_t)buffer * batch * padded;
+        float* x_to = x_rows + (size_t)buffer * batch * columns;
+        if (vectors) {
+            const int quads = N / 4;
+            for (int i = threadIdx.x; i < count * quads; i += blockDim.x) {
+                const int t = i / quads, n = (i % quads) * 4;
+                const float* r = xbc + (size_t)(first + t) * row_width + inner + group * N + n;
+                const int where = t * padded + ((((n % per) >> 2) * lanes_per_column + n / per) << 2);
+                cp_async_f4(b_to + where, r);
+                if (MODE != SSM_LOCAL) cp_async_f4(c_to + where, r + groups * N);
+            }
+        } else {
+            for (int i = threadIdx.x; i < count * N; i += blockDim.x) {
+                const int t = i / N, n = i % N;
+                const float* r = xbc + (size_t)(first + t) * row_width + inner + group * N + n;
+                const int at = n % per;
+                const int where = t * padded + (((at >> 2) * lanes_per_column + n / per) << 2) + (at & 3);
+                cp_async_f1(b_to + where, r);
+                if (MODE != SSM_LOCAL) cp_async_f1(c_to + where, r + groups * N);
+            }
         }
         for (int i = threadIdx.x; i < count * columns; i += blockDim.x) {
             const int t = i / columns, c = i % columns;
-            x_rows[i] = slice * columns + c < P ? xbc[(size_t)(first + t) * row_width + head * P + slice * columns + c] : 0.0f;
+            if (slice * columns + c < P) cp_async_f1(x_to + i, xbc + (size_t)(first + t) * row_width + head * P + slice * columns + c);
+            else x_to[i] = 0.0f;
         }
-        if (threadIdx.x < count) {
-            const float dt = softplus_f(dt_in[(size_t)(first + threadIdx.x) * dt_stride + head] + bias);
-            dt_rows[threadIdx.x] = dt;
-            decay_rows[threadIdx.x] = expf(rate * dt);
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+    auto step_sizes = [&](int buffer, int count, float raw) {
+        if ((int)threadIdx.x < count) {
+            const float dt = softplus_f(raw + bias);
+            dt_rows[buffer * batch + threadIdx.x] = dt;
+            decay_rows[buffer * batch + threadIdx.x] = expf(rate * dt);
+        }
+    };
+    {
+        const int count = min(batch, end_row - start_row);
+        __syncthreads();                                             // the zeros are written
+        fetch(0, start_row, count);
+        step_sizes(0, count, (int)threadIdx.x < count ? dt_in[(size_t)(start_row + threadIdx.x) * dt_stride + head] : 0.0f);
+    }
+    int buffer = 0;
+    for (int first = start_row; first < end_row; first += batch, buffer ^= 1) {
+        const int count = min(batch, end_row - first);
+        const int next_count = min(batch, end_row - (first + batch));
+        float next_raw = 0.0f;
+        if (next_count > 0) {
+            fetch(buffer ^ 1, first + batch, next_count);
+            if ((int)threadIdx.x < next_count) next_raw = dt_in[(size_t)(first + batch + threadIdx.x) * dt_stride + head];
+            asm volatile("cp.async.wait_group 1;\n" ::);
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::);
         }
         __syncthreads();
+        const float* b_from = b_rows + (size_t)buffer * batch * padded;
+        const float* c_from = c_rows + (size_t)buffer * batch * padded;
+        const float* x_from = x_rows + (size_t)buffer * batch * columns;
         for (int t = 0; t < count; ++t) {
-            const float x = column < columns ? x_rows[t * columns + column] : 0.0f;
-            const float decay = decay_rows[t], dx = dt_rows[t] * x;
+            const float x = column < columns ? x_from[t * columns + column] : 0.0f;
+            const float decay = decay_rows[buffer * batch + t], dx = dt_rows[buffer * batch + t] * x;
             if (MODE == SSM_LOCAL) decays *= decay;
             float sum = 0.0f;
 #pragma unroll
             for (int v = 0; v < SSM_PER_LANE / 4; ++v) {
-                const float4 b = *reinterpret_cast<const float4*>(b_rows + t * padded + ((v * lanes_per_column + s) << 2));
+                const float4 b = *reinterpret_cast<const float4*>(b_from + t * padded + ((v * lanes_per_column + s) << 2));
                 S[4 * v + 0] = decay * S[4 * v + 0] + dx * b.x;
                 S[4 * v + 1] = decay * S[4 * v + 1] + dx * b.y;
                 S[4 * v + 2] = decay * S[4 * v + 2] + dx * b.z;
                 S[4 * v + 3] = decay * S[4 * v + 3] + dx * b.w;
                 if (MODE != SSM_LOCAL) {
-                    const float4 c = *reinterpret_cast<const float4*>(c_rows + t * padded + ((v * lanes_per_column + s) << 2));
+                    const float4 c = *reinterpret_cast<const float4*>(c_from + t * padded + ((v * lanes_per_column + s) << 2));
                     sum += S[4 * v + 0] * c.x + S[4 * v + 1] * c.y + S[4 * v + 2] * c.z + S[4 * v + 3] * c.w;
                 }
             }
@@ -202,6 +252,8 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, const float* __re
                 if (live && s == 0) y[(size_t)(first + t) * inner + head * P + p] = sum + skip * x;
             }
         }
+        step_sizes(buffer ^ 1, next_count, next_raw);
+        __syncthreads();                                             // this buffer is read; the next one's step sizes are written
     }
     if (MODE == SSM_LOCAL && threadIdx.x == 0 && slice == 0) chunk_decay[((size_t)seq * heads + head) * max_chunks + chunk] = decays;
     if ((MODE == SSM_LOCAL || (MODE == SSM_WHOLE && write_state)) && live) {
@@ -260,11 +312,11 @@ MRS_EXPORT int mrs_ssm_scan(const float* xbc, const float* dt_in, int dt_stride,
     if ((long long)heads * slices > 65535) return MRS_BAD_ARGUMENT;
     // rows a batch: what 40 KB of shared memory hold (several blocks share an SM), at least one, at most as many as threads
     const int row_floats = 2 * SSM_PER_LANE * lanes + columns + 2;
-    int batch = (40 * 1024 / 4) / row_floats;
+    int batch = (40 * 1024 / 4) / (2 * row_floats);       // two buffers
     if (batch > SSM_BATCH) batch = SSM_BATCH;
     if (batch > threads) batch = threads;
     if (batch < 1) batch = 1;
-    const size_t smem = (size_t)batch * row_floats * sizeof(float);
+    const size_t smem = (size_t)2 * batch * row_floats * sizeof(float);
     if (chunk_len == 0) {
         MRS_LAUNCH(ssm_scan_kernel<SSM_WHOLE>, dim3(sequences, heads * slices), threads, smem, stream, xbc, dt_in, dt_stride, dt_bias, a_log, d_skip,
                    ssm_state, state_stride, positions, q_start, state_slots, y, heads, groups, N, P, lanes, per, write_state,
