@@ -51,29 +51,37 @@ MRS_EXPORT int mrs_postnorm_add_norm(int is_bf16, float* stream, const float* br
 // gate_up [tokens, 2 * inter]: all gate columns, then all up columns.
 // ---------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void glu_clamped_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long total, int inter, float limit,
-                                   float alpha) {
+__global__ void glu_clamped_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int tokens, int inter, float limit, float alpha) {
     pdl_launch_dependents();
     pdl_wait();
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-        const long long t = i / inter;
-        const int c = (int)(i - t * inter);
-        const float g = fminf(to_float(gate_up[t * 2 * inter + c]), limit);
-        const float u = fminf(fmaxf(to_float(gate_up[t * 2 * inter + inter + c]), -limit), limit);
-        out[i] = from_float<T>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+    // a thread keeps its two columns and walks down the tokens: no division, neighbouring threads read neighbouring pairs
+    const int c = 2 * (blockIdx.x * blockDim.x + threadIdx.x);
+    if (c >= inter) return;
+    const bool pair = c + 1 < inter;
+    for (int t = blockIdx.y; t < tokens; t += gridDim.y) {
+        const T* row = gate_up + (size_t)t * 2 * inter;
+        T* o = out + (size_t)t * inter;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            if (j == 1 && !pair) break;
+            const float g = fminf(to_float(row[c + j]), limit);
+            const float u = fminf(fmaxf(to_float(row[inter + c + j]), -limit), limit);
+            o[c + j] = from_float<T>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+        }
     }
 }
 
 MRS_EXPORT int mrs_glu_clamped(int is_bf16, const void* gate_up, void* out, int tokens, int inter, float limit, float alpha, void* s) {
-    const long long total = (long long)tokens * inter;
-    if (total <= 0) return 0;
-    long long blocks = (total + 255) / 256;
-    const long long cap = (long long)mrs_sm_count() * 16;
-    if (blocks > cap) blocks = cap;
+    if (tokens <= 0 || inter <= 0) return 0;
+    const int threads = 128;
+    const unsigned across = (unsigned)((inter + 2 * threads - 1) / (2 * threads));
+    long long down = ((long long)mrs_sm_count() * 32 + across - 1) / across;
+    if (down > tokens) down = tokens;
+    if (down > 65535) down = 65535;
     if (is_bf16)
-        MRS_LAUNCH(glu_clamped_kernel<bf16>, (unsigned)blocks, 256, 0, s, (const bf16*)gate_up, (bf16*)out, total, inter, limit, alpha);
+        MRS_LAUNCH(glu_clamped_kernel<bf16>, dim3(across, (unsigned)down), threads, 0, s, (const bf16*)gate_up, (bf16*)out, tokens, inter, limit, alpha);
     else
-        MRS_LAUNCH(glu_clamped_kernel<float>, (unsigned)blocks, 256, 0, s, (const float*)gate_up, (float*)out, total, inter, limit, alpha);
+        MRS_LAUNCH(glu_clamped_kernel<float>, dim3(across, (unsigned)down), threads, 0, s, (const float*)gate_up, (float*)out, tokens, inter, limit, alpha);
     MRS_RETURN_LAUNCH_STATUS();
 }
 

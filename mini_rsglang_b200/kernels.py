@@ -1212,18 +1212,22 @@ def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dt_bias, a_log, d_skip, ssm_st
 
 
 def ssm_chunk_length(tokens: int, sequences: int, heads: int, n_state: int, head_dim: int, sms: int) -> int:
-    """Rows of a chunk of the recurrence, 0 for none, from a step's shapes alone (a recorded step keeps its choice): chunks
-    pay twice the arithmetic for blocks that run side by side, so they are taken where the sequences' own blocks (one a
-    head and slice of 128 threads, four to an SM) fill less than a quarter of the GPU and the portions are long."""
+    """Rows of a chunk of the recurrence, 0 for none, from a step's shapes alone (a recorded step keeps its choice).
+    A block (a head's slice of columns, 128 threads) walks its rows one after the other and waits most of the time, so
+    long portions are cut into chunks that run side by side, at the price of walking every row twice: measured on a
+    B200 with 64 heads of 64 columns and a state of 128 (256 blocks a sequence), 2,048 rows take 1,034 us in one go and
+    847, 783, 680, 658 us in chunks of 1,024, 512, 256 and 128 rows (with 64 the pass between the two costs what they
+    save).  So: about fourteen blocks an SM, chunks of at least 128 rows, only for portions of 512 rows and more."""
+    if os.environ.get("MRS_SSM_CHUNK"):             # the variable: for measuring other chunk lengths
+        return int(os.environ["MRS_SSM_CHUNK"]) if tokens >= 512 and tokens >= 128 * sequences else 0
     lanes = 1
     while lanes < 32 and -(-n_state // lanes) > 16:
         lanes *= 2
     slices = -(-head_dim // max(1, min(128 // lanes, head_dim)))
     blocks = sequences * heads * slices
-    room = 4 * sms
-    if tokens < 512 or tokens < 128 * sequences or 4 * blocks > room:
+    if tokens < 512 or tokens < 128 * sequences:
         return 0
-    chunks = min(room // blocks, tokens // 64)
+    chunks = min(-(-14 * sms // blocks), tokens // 128)
     if chunks < 2:
         return 0
     rows = -(-tokens // chunks)
