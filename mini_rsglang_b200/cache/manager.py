@@ -27,6 +27,7 @@ def host_api() -> ctypes.CDLL:
         "mrs_last_error": (ctypes.c_char_p, []),
         "mrs_cache_create": (c_vp, [c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int), p_i64, c_int, c_int]),
         "mrs_cache_create_sharing": (c_vp, [c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int), p_i64, c_int, c_int]),
+        "mrs_cache_create_keeping": (c_vp, [c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int), ctypes.POINTER(c_int), p_i64, c_int, c_int]),
         "mrs_cache_destroy": (None, [c_vp]),
         "mrs_cache_open_prompt": (c_int, [c_vp, c_i64, c_vp, c_i64, c_i64, c_i64, p_i64]),
         "mrs_cache_publish": (c_int, [c_vp, c_i64, c_vp, c_i64]),
@@ -80,11 +81,13 @@ def last_error(lib) -> str:
 
 @dataclass(frozen=True)
 class CacheGroup:
-    """Layers with the same need of the cache: every key ("full") or the last `window`."""
+    """Layers with the same need of the cache: every key ("full") or the last `window`, with the pages of the first
+    `keep_first` positions kept beside them."""
 
     kind: str = "full"
     window: int = 0
     num_pages: int = 0
+    keep_first: int = 0
 
 
 class CacheManager:
@@ -112,8 +115,12 @@ class CacheManager:
         pages = (ctypes.c_int64 * n)(*[int(g.num_pages) for g in groups])
         if prefix_cache and any(g.kind != "full" for g in groups):
             raise InvalidRequest("prefix sharing needs layers that keep all their keys: a window of keys cannot be shared")
-        create = self.lib.mrs_cache_create_sharing if prefix_cache else self.lib.mrs_cache_create
-        self.handle = create(n, kinds, windows, pages, self.page_size, self.max_slots)
+        if any(g.keep_first for g in groups):
+            keeps = (ctypes.c_int * n)(*[int(g.keep_first) for g in groups])
+            self.handle = self.lib.mrs_cache_create_keeping(n, kinds, windows, keeps, pages, self.page_size, self.max_slots)
+        else:
+            create = self.lib.mrs_cache_create_sharing if prefix_cache else self.lib.mrs_cache_create
+            self.handle = create(n, kinds, windows, pages, self.page_size, self.max_slots)
         self.prefix_cache = bool(prefix_cache)
         if not self.handle:
             raise InvalidRequest(f"cache manager: {last_error(self.lib)}")

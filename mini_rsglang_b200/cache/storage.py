@@ -21,15 +21,15 @@ class CacheEntry:
     state: torch.Tensor | None = None  # [slots, *shape]
 
 
-def plan_groups(needs: list[KVNeed | None]) -> tuple[list[tuple[str, int]], list[int]]:
-    """Distinct (kind, window) among the needs, and each need's group index (-1 for None)."""
-    keys: list[tuple[str, int]] = []
+def plan_groups(needs: list[KVNeed | None]) -> tuple[list[tuple[str, int, int]], list[int]]:
+    """Distinct (kind, window, kept first positions) among the needs, and each need's group index (-1 for None)."""
+    keys: list[tuple[str, int, int]] = []
     index = []
     for need in needs:
         if need is None:
             index.append(-1)
             continue
-        key = (need.kind, need.window if need.kind == "window" else 0)
+        key = (need.kind, need.window if need.kind == "window" else 0, need.keep_first if need.kind == "window" else 0)
         if key not in keys:
             keys.append(key)
         index.append(keys.index(key))

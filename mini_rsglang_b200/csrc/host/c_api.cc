@@ -29,11 +29,12 @@ API const char* mrs_last_error() { return g_error.c_str(); }
 
 // ----------------------------------------------------------------------------- cache manager
 static void* cache_create(int n_groups, const int* kinds, const int* windows, const int64_t* num_pages, int page_size,
-                          int max_slots, bool prefix_cache) {
+                          int max_slots, bool prefix_cache, const int* keep_first = nullptr) {
     try {
         std::vector<mrs::GroupSpec> groups;
         for (int g = 0; g < n_groups; ++g)
-            groups.push_back({kinds[g] == 1 ? mrs::GroupKind::Window : mrs::GroupKind::Full, windows[g], num_pages[g]});
+            groups.push_back({kinds[g] == 1 ? mrs::GroupKind::Window : mrs::GroupKind::Full, windows[g], num_pages[g],
+                              keep_first ? keep_first[g] : 0});
         return new mrs::CacheManager(std::move(groups), page_size, max_slots, prefix_cache);
     } catch (const std::exception& e) {
         g_error = e.what();
@@ -43,6 +44,11 @@ static void* cache_create(int n_groups, const int* kinds, const int* windows, co
 API void* mrs_cache_create(int n_groups, const int* kinds, const int* windows, const int64_t* num_pages,
                            int page_size, int max_slots) {
     return cache_create(n_groups, kinds, windows, num_pages, page_size, max_slots, false);
+}
+// Window groups may keep the pages of their first `keep_first[g]` positions for a request's whole life.
+API void* mrs_cache_create_keeping(int n_groups, const int* kinds, const int* windows, const int* keep_first,
+                                   const int64_t* num_pages, int page_size, int max_slots) {
+    return cache_create(n_groups, kinds, windows, num_pages, page_size, max_slots, false, keep_first);
 }
 // The same with prefix sharing between requests (every group must keep all keys).
 API void* mrs_cache_create_sharing(int n_groups, const int* kinds, const int* windows, const int64_t* num_pages,

@@ -40,6 +40,7 @@ CacheManager::CacheManager(std::vector<GroupSpec> groups, int page_size, int max
     for (const auto& g : groups_) {
         if (g.num_pages <= 0 || g.num_pages > INT32_MAX) throw std::invalid_argument("invalid page count");
         if (g.kind == GroupKind::Window && g.window <= 0) throw std::invalid_argument("window group needs a window");
+        if (g.keep_first < 0 || (g.keep_first > 0 && g.kind != GroupKind::Window)) throw std::invalid_argument("kept first positions go with a window");
         pools_.emplace_back(g.num_pages);
     }
     reserved_.assign(groups_.size(), 0);
@@ -70,13 +71,18 @@ int64_t CacheManager::first_needed_page(int g, int64_t next_position) const {
     return first_key / page_size_;
 }
 
+// Logical pages that hold kept first positions: a request holds them for all its life.
+int64_t CacheManager::kept_pages(int g) const {
+    return groups_[g].kind == GroupKind::Window ? ceil_div(groups_[g].keep_first, page_size_) : 0;
+}
+
 int64_t CacheManager::worst_case_pages(int g, int64_t tokens, int64_t max_step) const {
     const int64_t all = ceil_div(tokens, page_size_);
     if (groups_[g].kind == GroupKind::Full) return all;
     // before a step of n tokens from position s the pages from first_needed_page(s) to the one of
     // s + n - 1 are live: at most window - 1 + max_step keys, which touch at most this many pages
     const int64_t span = (int64_t)groups_[g].window - 1 + std::max<int64_t>(1, max_step);
-    return std::min(all, ceil_div(span, page_size_) + 1);
+    return std::min(all, ceil_div(span, page_size_) + 1 + kept_pages(g));
 }
 
 // What is still promised to a request in group g: enough to reach its worst case, but never more
@@ -216,7 +222,7 @@ int CacheManager::trim(int64_t request, int64_t computed) {
         if (groups_[g].kind != GroupKind::Window) continue;
         auto& table = lease.tables[g];
         const int64_t keep_from = std::min<int64_t>(first_needed_page((int)g, computed), (int64_t)table.size());
-        for (int64_t p = lease.first_live[g]; p < keep_from; ++p) {
+        for (int64_t p = std::max(lease.first_live[g], kept_pages((int)g)); p < keep_from; ++p) {
             if (table[(size_t)p] >= 0) {
                 pools_[g].release(table[(size_t)p]);
                 table[(size_t)p] = -1;
@@ -278,7 +284,7 @@ std::string CacheManager::check() const {
                 const int32_t page = lease.tables[g][p];
                 if (page < 0) continue;
                 if (page >= pool.total()) { bad << "group " << g << ": request " << id << " holds page " << page << " outside the pool; "; continue; }
-                if ((int64_t)p < lease.first_live[g]) bad << "group " << g << ": request " << id << " holds logical page " << p << " below its live range; ";
+                if ((int64_t)p < lease.first_live[g] && (int64_t)p >= kept_pages((int)g)) bad << "group " << g << ": request " << id << " holds logical page " << p << " below its live range; ";
                 expected[(size_t)page] += 1;
             }
         }

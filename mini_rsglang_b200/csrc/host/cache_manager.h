@@ -3,8 +3,8 @@
 //
 // Layers with the same need share a *group*: its own pool of pages and, for every open
 // request, its own block table.  A "full" group keeps every key of a request; a "window" group
-// keeps only the pages that the last `window` positions still touch and gives the others
-// back while the request runs.  Beside the pages, every open request holds one *state slot*:
+// keeps only the pages that the last `window` positions still touch (and, with `keep_first`, the
+// pages of the first positions) and gives the others back while the request runs.  Beside the pages, every open request holds one *state slot*:
 // an index into per-request arrays of fixed size (recurrent state, sampler state).
 //
 // Reference: PagePool, PageLease and CacheManager of crates/cache/src/lib.rs:242-410
@@ -30,6 +30,7 @@ struct GroupSpec {
     GroupKind kind;
     int window;          // positions a query may look back (Window groups); 0 for Full
     int64_t num_pages;   // size of this group's pool
+    int keep_first = 0;  // Window groups: the first positions stay in sight of every query, so their pages are never given back
 };
 
 class PagePool {
@@ -124,6 +125,7 @@ public:
 
 private:
     int64_t first_needed_page(int g, int64_t next_position) const;
+    int64_t kept_pages(int g) const;
     void settle_promise(Lease& lease, int g);
     int64_t evict(int64_t nodes);
     std::unique_ptr<PrefixTree> tree_;

@@ -117,23 +117,23 @@ class ModelRunner:
         kv_needs, state_needs = self.model.kv_needs(), self.model.state_needs()
         keys, group_of = plan_groups(kv_needs)
         if not keys:                       # a model without paged caches still has block tables of width 0
-            keys = [("full", 0)]
+            keys = [("full", 0, 0)]
         element = 4 if runtime.dtype is torch.float32 else 2
         groups = []
-        for g, (kind, window) in enumerate(keys):
+        for g, (kind, window, keep_first) in enumerate(keys):
             per_page = bytes_per_page(kv_needs, group_of, g, limits.page_size, element)
             if num_pages is not None:
                 pages = int(num_pages)
             elif kind == "window":
                 span = window - 1 + limits.prefill_budget
-                pages = limits.max_running * (-(-span // limits.page_size) + 1)
+                pages = limits.max_running * (-(-span // limits.page_size) + 1 + -(-keep_first // limits.page_size))
             else:
                 if kv_bytes is None:
                     raise InvalidRequest("give kv_bytes or num_pages")
                 pages = int(kv_bytes) // max(per_page, 1)
             if pages <= 0 or pages > 2**31 - 1:
                 raise InvalidRequest("invalid KV memory budget")
-            groups.append(CacheGroup(kind, window, pages))
+            groups.append(CacheGroup(kind, window, pages, keep_first))
         self.groups = groups
         if limits.prefix_cache and (any(g.kind != "full" for g in groups) or any(need is not None for need in state_needs)):
             raise InvalidRequest("prefix sharing needs a model whose layers keep all their keys and no state of their "

@@ -107,9 +107,10 @@ class BiasedWindowAttention(Mixer):
         return specs
 
     def cache_need(self):
-        # A window that keeps first positions holds on to their pages: the group keeps every page.
-        kind = "window" if self.window and not self.keep_first else "full"
-        return KVNeed(self.nkv, self.d, kind, self.window if kind == "window" else 0, value_dim=self.e)
+        # a window gives passed pages back; the pages of kept first positions stay with the request
+        if self.window:
+            return KVNeed(self.nkv, self.d, "window", self.window, value_dim=self.e, keep_first=self.keep_first)
+        return KVNeed(self.nkv, self.d, "full", 0, value_dim=self.e)
 
     def bind(self, tensors, runtime):
         super().bind(tensors, runtime)

@@ -67,6 +67,7 @@ class KVNeed:
     kind: str = "full"       # "full" | "window"
     window: int = 0
     value_dim: int = 0       # elements of a value head where they differ from a key head's (0: head_dim)
+    keep_first: int = 0      # "window": the first positions stay in sight, their pages are kept
 
     @property
     def v_head_dim(self) -> int:

@@ -98,3 +98,30 @@ def test_chunks_of_the_recurrence_are_chosen_from_shapes():
     n = ssm_chunk_length(2048, 1, 4, 32, 48, 148)
     assert n == 128
     assert ssm_chunk_length(2048, 32, 4, 32, 48, 148) == 0           # many short portions
+
+
+def test_window_group_keeps_the_pages_of_the_first_positions():
+    """A window of 6 positions with the first 5 kept, pages of 4: logical pages 0 and 1 stay for the request's whole life,
+    the pages between them and the window go back to the pool as the request grows, and every page comes back at its end."""
+    from mini_rsglang_b200.cache.manager import CacheGroup, CacheManager
+
+    m = CacheManager([CacheGroup("window", 6, 9, keep_first=5)], page_size=4, max_slots=2)
+    assert m.worst_case_pages(0, 1000, 1) == 2 + 1 + 2             # the window's span, and the two kept pages
+    m.open(1)
+    held = []
+    for length in range(1, 33):
+        m.extend(1, length)
+        m.trim(1, length)
+        table = m.table(1)
+        assert (table[:min(2, len(table))] >= 0).all(), "a kept page was given back"
+        first_key = max(0, length - 6 + 1)
+        for page, physical in enumerate(table):
+            needed = page < 2 or (page + 1) * 4 > first_key
+            assert (physical >= 0) == needed, (length, page, table)
+        held.append(int((table >= 0).sum()))
+        m.check_integrity()
+    assert max(held) <= 5 and m.free_pages(0) == 9 - held[-1]
+    m.close(1)
+    assert m.free_pages(0) == 9
+    with pytest.raises(InvalidRequest):
+        CacheManager([CacheGroup("full", 0, 9, keep_first=5)], page_size=4, max_slots=2)
