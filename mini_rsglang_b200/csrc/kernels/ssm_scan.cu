@@ -96,8 +96,8 @@ MRS_EXPORT int mrs_causal_conv_silu(const float* in, int in_stride, int offset, 
 }
 
 // ---------------------------------------------------------------------------------------------
-// The recurrence, token by token.  One block per (sequence, head, slice of the head's columns); thread (p, s): column p
-// of S and the rows n = s * per + i of it in registers (lanes of one p are neighbours, so that y's sum over n is a few shuffles).
+// The recurrence, token by token.  One block per (sequence, head, slice of the head's columns); thread (p, s): two
+// neighbouring columns p, p + 1 of S and the rows n = s * per + i of them in registers (lanes of one p are neighbours, so that y's sum over n is a few shuffles).
 // xbc [tokens, heads * P + 2 * groups * N] float32 (x | B | C after convolution and silu), raw dt a column range of
 // the projection's rows, y [tokens, heads * P] float32.  ssm_state [slots, heads, N, P].
 // ---------------------------------------------------------------------------------------------
@@ -116,6 +116,7 @@ enum { SSM_WHOLE = 0, SSM_LOCAL = 1, SSM_FINAL = 2 };
 // padded with zeros to 16 elements a lane: a thread reads its 16 values as four vectors, and the lanes of a warp read
 // neighbouring vectors.
 #define SSM_BATCH 16
+#define SSM_COLUMNS 2           // columns of S a thread owns
 
 __device__ __forceinline__ void cp_async_f4(float* to, const float* from) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(to)), "l"(from));
@@ -142,8 +143,11 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, const float* __re
     const int start_row = MODE == SSM_WHOLE ? seq_start : seq_start + chunk * chunk_len;
     const int end_row = MODE == SSM_WHOLE ? seq_end : min(seq_end, start_row + chunk_len);
     if (start_row >= end_row) return;
-    const int s = threadIdx.x % lanes_per_column, column = threadIdx.x / lanes_per_column, p = slice * columns + column;
-    const bool live = p < P && column < columns;
+    // a thread owns SSM_COLUMNS neighbouring columns: what it reads of B and C serves them all
+    const int s = threadIdx.x % lanes_per_column, column = (threadIdx.x / lanes_per_column) * SSM_COLUMNS, p = slice * columns + column;
+    bool live[SSM_COLUMNS];
+#pragma unroll
+    for (int j = 0; j < SSM_COLUMNS; ++j) live[j] = p + j < P && column + j < columns;
     const int group = head / (heads / groups);
     const int inner = heads * P, row_width = inner + 2 * groups * N;
     const int n0 = s * per;
@@ -159,11 +163,13 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, const float* __re
 
     float* state = MODE == SSM_WHOLE ? ssm_state + (long long)slot * state_stride + (size_t)head * N * P
                                      : chunk_state + (((size_t)seq * heads + head) * max_chunks + chunk) * N * P;
-    float S[SSM_PER_LANE];
+    float S[SSM_COLUMNS][SSM_PER_LANE];
     const bool zero = MODE == SSM_LOCAL || (MODE == SSM_WHOLE && positions[seq_start] == 0);
 #pragma unroll
-    for (int i = 0; i < SSM_PER_LANE; ++i)
-        S[i] = (!zero && live && i < per && n0 + i < N) ? state[(size_t)(n0 + i) * P + p] : 0.0f;
+    for (int j = 0; j < SSM_COLUMNS; ++j)
+#pragma unroll
+        for (int i = 0; i < SSM_PER_LANE; ++i)
+            S[j][i] = (!zero && live[j] && i < per && n0 + i < N) ? state[(size_t)(n0 + i) * P + p + j] : 0.0f;
     const float bias = dt_bias[head], rate = -expf(a_log[head]), skip = d_skip[head];
     float decays = 1.0f;
 
@@ -231,35 +237,48 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, const float* __re
         const float* c_from = c_rows + (size_t)buffer * batch * padded;
         const float* x_from = x_rows + (size_t)buffer * batch * columns;
         for (int t = 0; t < count; ++t) {
-            const float x = column < columns ? x_from[t * columns + column] : 0.0f;
-            const float decay = decay_rows[buffer * batch + t], dx = dt_rows[buffer * batch + t] * x;
+            const float decay = decay_rows[buffer * batch + t], dt = dt_rows[buffer * batch + t];
+            float x[SSM_COLUMNS], dx[SSM_COLUMNS], sum[SSM_COLUMNS];
+#pragma unroll
+            for (int j = 0; j < SSM_COLUMNS; ++j) {
+                x[j] = column + j < columns ? x_from[t * columns + column + j] : 0.0f;
+                dx[j] = dt * x[j];
+                sum[j] = 0.0f;
+            }
             if (MODE == SSM_LOCAL) decays *= decay;
-            float sum = 0.0f;
 #pragma unroll
             for (int v = 0; v < SSM_PER_LANE / 4; ++v) {
                 const float4 b = *reinterpret_cast<const float4*>(b_from + t * padded + ((v * lanes_per_column + s) << 2));
-                S[4 * v + 0] = decay * S[4 * v + 0] + dx * b.x;
-                S[4 * v + 1] = decay * S[4 * v + 1] + dx * b.y;
-                S[4 * v + 2] = decay * S[4 * v + 2] + dx * b.z;
-                S[4 * v + 3] = decay * S[4 * v + 3] + dx * b.w;
-                if (MODE != SSM_LOCAL) {
-                    const float4 c = *reinterpret_cast<const float4*>(c_from + t * padded + ((v * lanes_per_column + s) << 2));
-                    sum += S[4 * v + 0] * c.x + S[4 * v + 1] * c.y + S[4 * v + 2] * c.z + S[4 * v + 3] * c.w;
+                float4 c = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (MODE != SSM_LOCAL) c = *reinterpret_cast<const float4*>(c_from + t * padded + ((v * lanes_per_column + s) << 2));
+#pragma unroll
+                for (int j = 0; j < SSM_COLUMNS; ++j) {
+                    S[j][4 * v + 0] = decay * S[j][4 * v + 0] + dx[j] * b.x;
+                    S[j][4 * v + 1] = decay * S[j][4 * v + 1] + dx[j] * b.y;
+                    S[j][4 * v + 2] = decay * S[j][4 * v + 2] + dx[j] * b.z;
+                    S[j][4 * v + 3] = decay * S[j][4 * v + 3] + dx[j] * b.w;
+                    if (MODE != SSM_LOCAL)
+                        sum[j] += S[j][4 * v + 0] * c.x + S[j][4 * v + 1] * c.y + S[j][4 * v + 2] * c.z + S[j][4 * v + 3] * c.w;
                 }
             }
             if (MODE != SSM_LOCAL) {
-                for (int o = 1; o < lanes_per_column; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-                if (live && s == 0) y[(size_t)(first + t) * inner + head * P + p] = sum + skip * x;
+#pragma unroll
+                for (int j = 0; j < SSM_COLUMNS; ++j) {
+                    for (int o = 1; o < lanes_per_column; o <<= 1) sum[j] += __shfl_xor_sync(0xffffffffu, sum[j], o);
+                    if (live[j] && s == 0) y[(size_t)(first + t) * inner + head * P + p + j] = sum[j] + skip * x[j];
+                }
             }
         }
         step_sizes(buffer ^ 1, next_count, next_raw);
         __syncthreads();                                             // this buffer is read; the next one's step sizes are written
     }
     if (MODE == SSM_LOCAL && threadIdx.x == 0 && slice == 0) chunk_decay[((size_t)seq * heads + head) * max_chunks + chunk] = decays;
-    if ((MODE == SSM_LOCAL || (MODE == SSM_WHOLE && write_state)) && live) {
+    if (MODE == SSM_LOCAL || (MODE == SSM_WHOLE && write_state)) {
 #pragma unroll
-        for (int i = 0; i < SSM_PER_LANE; ++i)
-            if (i < per && n0 + i < N) state[(size_t)(n0 + i) * P + p] = S[i];
+        for (int j = 0; j < SSM_COLUMNS; ++j)
+#pragma unroll
+            for (int i = 0; i < SSM_PER_LANE; ++i)
+                if (live[j] && i < per && n0 + i < N) state[(size_t)(n0 + i) * P + p + j] = S[j][i];
     }
 }
 
@@ -308,7 +327,7 @@ MRS_EXPORT int mrs_ssm_scan(const float* xbc, const float* dt_in, int dt_stride,
     int columns = 128 / lanes;
     if (columns > P) columns = P;
     const int slices = (P + columns - 1) / columns;
-    const int threads = (columns * lanes + 31) / 32 * 32;
+    const int threads = ((columns + SSM_COLUMNS - 1) / SSM_COLUMNS * lanes + 31) / 32 * 32;
     if ((long long)heads * slices > 65535) return MRS_BAD_ARGUMENT;
     // rows a batch: what 40 KB of shared memory hold (several blocks share an SM), at least one, at most as many as threads
     const int row_floats = 2 * SSM_PER_LANE * lanes + columns + 2;
