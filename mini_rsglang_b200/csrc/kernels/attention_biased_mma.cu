@@ -23,7 +23,7 @@ constexpr int D = MRS_HEAD_DIM, E = MRS_VALUE_DIM;
 static_assert(D % 16 == 0 && D >= 16 && D <= 256 && E % 16 == 0 && E >= 16 && E <= 256, "head sizes: multiples of 16 up to 256");
 constexpr int THREADS = 128;
 constexpr int ROWS_WIDE = 64, ROWS_NARROW = 16;
-constexpr int KV_WIDE = (D <= 128 && E <= 128) ? 64 : 32;
+constexpr int KV_WIDE = 32;            // keys a block in rows mode: small blocks leave room for three or four CTAs an SM
 constexpr int KV_NARROW = 64;
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -55,10 +55,6 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
-
-// tanh(z) = 1 - 2 / (exp(2 z) + 1) with the hardware's exponential and reciprocal: a few instructions a score where
-// the library's tanhf takes dozens; its absolute error, about 1e-6 here, is far below what bfloat16 keys leave of a score.
-__device__ __forceinline__ float fast_tanh(float z) { return 1.0f - __fdividef(2.0f, __expf(2.0f * z) + 1.0f); }
 
 struct Tile { int seq, first_token, tokens, pad; };
 
@@ -159,7 +155,7 @@ __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[E / 8
             float v = -CUDART_INF_F;
             if (seen) {
                 v = s[nt][e] * x.scale;
-                if (x.cap > 0.0f) v = x.cap * fast_tanh(v / x.cap);
+                if (x.cap > 0.0f) v = x.cap * tanhf(v / x.cap);
                 if (x.bias) v += x.bias[(size_t)min(back, x.bias_rows - 1) * nq + row_head[e >> 1]];
                 v *= LOG2E;
             }

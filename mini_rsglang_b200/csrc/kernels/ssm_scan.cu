@@ -96,8 +96,8 @@ MRS_EXPORT int mrs_causal_conv_silu(const float* in, int in_stride, int offset, 
 }
 
 // ---------------------------------------------------------------------------------------------
-// The recurrence, token by token.  One block per (sequence, head, slice of the head's columns); thread (p, s): two
-// neighbouring columns p, p + 1 of S and the rows n = s * per + i of them in registers (lanes of one p are neighbours, so that y's sum over n is a few shuffles).
+// The recurrence, token by token.  One block per (sequence, head, slice of the head's columns); thread (p, s): column p
+// of S (SSM_COLUMNS neighbouring ones) and the rows n = s * per + i of it in registers (lanes of one p are neighbours, so that y's sum over n is a few shuffles).
 // xbc [tokens, heads * P + 2 * groups * N] float32 (x | B | C after convolution and silu), raw dt a column range of
 // the projection's rows, y [tokens, heads * P] float32.  ssm_state [slots, heads, N, P].
 // ---------------------------------------------------------------------------------------------
@@ -116,7 +116,7 @@ enum { SSM_WHOLE = 0, SSM_LOCAL = 1, SSM_FINAL = 2 };
 // padded with zeros to 16 elements a lane: a thread reads its 16 values as four vectors, and the lanes of a warp read
 // neighbouring vectors.
 #define SSM_BATCH 16
-#define SSM_COLUMNS 2           // columns of S a thread owns
+#define SSM_COLUMNS 1           // columns of S a thread owns (two were measured and are slower: 518 against 446 us for 2,048 rows in chunks)
 
 __device__ __forceinline__ void cp_async_f4(float* to, const float* from) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(to)), "l"(from));
@@ -181,7 +181,16 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, const float* __re
         float* b_to = b_rows + (size_t)buffer * batch * padded;
         float* c_to = c_rows + (size_t)buffer * batch * padded;
         float* x_to = x_rows + (size_t)buffer * batch * columns;
-        if (vectors) {
+        if (vectors && blockDim.x % (N / 4) == 0) {
+            // a thread's place in a row is the same in every round: the divisions are done once
+            const int quads = N / 4, n = ((int)threadIdx.x % quads) * 4, step = blockDim.x / quads;
+            const int where = ((((n % per) >> 2) * lanes_per_column + n / per) << 2);
+            const float* r = xbc + (size_t)first * row_width + inner + group * N + n;
+            for (int t = threadIdx.x / quads; t < count; t += step) {
+                cp_async_f4(b_to + t * padded + where, r + (size_t)t * row_width);
+                if (MODE != SSM_LOCAL) cp_async_f4(c_to + t * padded + where, r + (size_t)t * row_width + groups * N);
+            }
+        } else if (vectors) {
             const int quads = N / 4;
             for (int i = threadIdx.x; i < count * quads; i += blockDim.x) {
                 const int t = i / quads, n = (i % quads) * 4;
@@ -200,10 +209,18 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, const float* __re
                 if (MODE != SSM_LOCAL) cp_async_f1(c_to + where, r + groups * N);
             }
         }
-        for (int i = threadIdx.x; i < count * columns; i += blockDim.x) {
-            const int t = i / columns, c = i % columns;
-            if (slice * columns + c < P) cp_async_f1(x_to + i, xbc + (size_t)(first + t) * row_width + head * P + slice * columns + c);
-            else x_to[i] = 0.0f;
+        if (blockDim.x % columns == 0) {
+            const int c = (int)threadIdx.x % columns, step = blockDim.x / columns;
+            for (int t = threadIdx.x / columns; t < count; t += step) {
+                if (slice * columns + c < P) cp_async_f1(x_to + t * columns + c, xbc + (size_t)(first + t) * row_width + head * P + slice * columns + c);
+                else x_to[t * columns + c] = 0.0f;
+            }
+        } else {
+            for (int i = threadIdx.x; i < count * columns; i += blockDim.x) {
+                const int t = i / columns, c = i % columns;
+                if (slice * columns + c < P) cp_async_f1(x_to + i, xbc + (size_t)(first + t) * row_width + head * P + slice * columns + c);
+                else x_to[i] = 0.0f;
+            }
         }
         asm volatile("cp.async.commit_group;\n" ::);
     };
