@@ -223,4 +223,6 @@ SPECIALISED_BUILDS = tuple((lambda d=d: specialised_kernel_library("attention_mm
     tuple((lambda d=d: specialised_kernel_library("attention_decode_tma.cu", {"MRS_HEAD_DIM": d})) for d in (64, 128)) + \
     tuple((lambda d=d: specialised_kernel_library("attention_prefill_tc.cu", {"MRS_HEAD_DIM": d})) for d in (64, 128)) + \
     (lambda: specialised_kernel_library("gemm_tc.cu", {}), lambda: specialised_kernel_library("gemm_many_rows.cu", {}),
-     hybrid_kernel_library)
+     hybrid_kernel_library,
+     lambda: specialised_kernel_library("attention_biased_mma.cu", {"MRS_HEAD_DIM": 128, "MRS_VALUE_DIM": 128}),
+     lambda: specialised_kernel_library("attention_biased_mma.cu", {"MRS_HEAD_DIM": 64, "MRS_VALUE_DIM": 32}))
