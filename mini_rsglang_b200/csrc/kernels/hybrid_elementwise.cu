@@ -34,11 +34,71 @@ __global__ void postnorm_add_norm_kernel(float* __restrict__ stream, const float
     for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_float<T>(res[i] * scale_v * w_next[i]);
 }
 
+// The same with the row kept in registers between the passes (width at most NORM_KEEP * blockDim.x): every element is
+// read once.  A thread takes the elements threadIdx.x, threadIdx.x + blockDim.x, ... in that order, as the kernel above does.
+#define NORM_KEEP 8
+template <typename T>
+__global__ void postnorm_add_norm_kept_kernel(float* __restrict__ stream, const float* __restrict__ branch,
+                                              const float* __restrict__ w_post, const float* __restrict__ w_next, float eps_post,
+                                              float eps_next, T* __restrict__ out, int width) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[33];
+    const size_t r = blockIdx.x;
+    float* res = stream + r * width;
+    const float* a = branch + r * width;
+    float av[NORM_KEEP], rv[NORM_KEEP], wv[NORM_KEEP];
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NORM_KEEP; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        av[j] = i < width ? a[i] : 0.0f;
+        sum += av[j] * av[j];
+    }
+#pragma unroll
+    for (int j = 0; j < NORM_KEEP; ++j) {                  // asked for before the block waits for its sum
+        const int i = threadIdx.x + j * blockDim.x;
+        rv[j] = i < width ? res[i] : 0.0f;
+        wv[j] = i < width ? w_post[i] : 0.0f;
+    }
+    const float scale_a = 1.0f / sqrtf(block_sum(sum, scratch) / (float)width + eps_post);
+    sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NORM_KEEP; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < width) {
+            rv[j] = rv[j] + av[j] * scale_a * wv[j];
+            res[i] = rv[j];
+            sum += rv[j] * rv[j];
+        }
+    }
+    if (w_next == nullptr) return;
+#pragma unroll
+    for (int j = 0; j < NORM_KEEP; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        wv[j] = i < width ? w_next[i] : 0.0f;
+    }
+    const float scale_v = 1.0f / sqrtf(block_sum(sum, scratch) / (float)width + eps_next);
+    T* o = out + r * width;
+#pragma unroll
+    for (int j = 0; j < NORM_KEEP; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < width) o[i] = from_float<T>(rv[j] * scale_v * wv[j]);
+    }
+}
+
 MRS_EXPORT int mrs_postnorm_add_norm(int is_bf16, float* stream, const float* branch, const float* w_post, const float* w_next,
                                      float eps_post, float eps_next, void* out, int rows, int width, void* s) {
     if (rows <= 0) return 0;
     if (width <= 0) return MRS_BAD_ARGUMENT;
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    if (width <= NORM_KEEP * threads) {
+        if (is_bf16)
+            MRS_LAUNCH(postnorm_add_norm_kept_kernel<bf16>, rows, threads, 0, s, stream, branch, w_post, w_next, eps_post, eps_next, (bf16*)out, width);
+        else
+            MRS_LAUNCH(postnorm_add_norm_kept_kernel<float>, rows, threads, 0, s, stream, branch, w_post, w_next, eps_post, eps_next, (float*)out, width);
+        MRS_RETURN_LAUNCH_STATUS();
+    }
     if (is_bf16)
         MRS_LAUNCH(postnorm_add_norm_kernel<bf16>, rows, threads, 0, s, stream, branch, w_post, w_next, eps_post, eps_next, (bf16*)out, width);
     else

@@ -15,36 +15,62 @@
 
 // in [tokens, in_stride] float32, the channels at column `offset`; conv_state [slots, (taps - 1), channels] with
 // `state_stride` floats from slot to slot; out [tokens, channels].
+// A thread keeps one channel and walks down SSM_CONV_ROWS rows with the last taps - 1 inputs in registers: where a row
+// follows the row before it in the same sequence, one input is loaded for it; at the block's first row and at a
+// sequence's first row of the step the inputs before it come from the rows above or from the slot's state.
+#define SSM_CONV_ROWS 16
+
+template <int MAX_TAPS>
 __global__ void causal_conv_silu_kernel(const float* __restrict__ in, int in_stride, int offset, const float* __restrict__ weight,
                                         const float* __restrict__ bias, const float* __restrict__ conv_state, long long state_stride,
                                         const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                                         const int* __restrict__ q_start, const int* __restrict__ state_slots,
-                                        float* __restrict__ out, int channels, int taps) {
+                                        float* __restrict__ out, int tokens, int channels, int taps) {
     pdl_launch_dependents();
     pdl_wait();
-    const int t = blockIdx.x;
-    const int seq = seq_of_token[t];
-    const int start_row = q_start[seq], end_row = q_start[seq + 1];
-    const int slot = state_slots[seq];
-    const int pos = positions[t];
-    const bool real = t >= start_row && t < end_row && slot >= 0;
-    const float* state = conv_state + (real ? (long long)slot * state_stride : 0);
-    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
-        float acc = 0.0f;
-        if (real) {
-            acc = bias ? bias[c] : 0.0f;
-            for (int k = 0; k < taps; ++k) {
-                const int back = taps - 1 - k;
-                if (pos - back < 0) continue;                       // before the sequence's start
-                const int row = t - back;
-                float x;
-                if (row >= start_row) x = in[(size_t)row * in_stride + offset + c];
-                else x = state[(size_t)(taps - 1 - (start_row - row)) * channels + c];     // the inputs of earlier steps
-                acc += weight[(size_t)c * taps + k] * x;
-            }
-            acc = acc / (1.0f + expf(-acc));
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
+    const int first = blockIdx.x * SSM_CONV_ROWS, last = min(tokens, first + SSM_CONV_ROWS);
+    float w[MAX_TAPS], history[MAX_TAPS];          // history[j]: the input taps - 1 - j rows back, j < taps - 1
+#pragma unroll
+    for (int k = 0; k < MAX_TAPS; ++k) w[k] = k < taps ? weight[(size_t)c * taps + k] : 0.0f;
+    const float b = bias ? bias[c] : 0.0f;
+    int previous_seq = -1;
+    for (int t = first; t < last; ++t) {
+        const int seq = seq_of_token[t];
+        const int start_row = q_start[seq], end_row = q_start[seq + 1];
+        const int slot = state_slots[seq];
+        if (t < start_row || t >= end_row || slot < 0) {          // a padding row
+            out[(size_t)t * channels + c] = 0.0f;
+            previous_seq = -1;
+            continue;
         }
-        out[(size_t)t * channels + c] = acc;
+        const int pos = positions[t];
+        if (seq != previous_seq || t == start_row) {              // the inputs before this row, afresh
+            const float* state = conv_state + (long long)slot * state_stride;
+#pragma unroll
+            for (int j = 0; j < MAX_TAPS - 1; ++j) {
+                const int back = taps - 1 - j, row = t - back;
+                float x = 0.0f;
+                if (j < taps - 1 && pos - back >= 0) x = row >= start_row ? in[(size_t)row * in_stride + offset + c]
+                                                          : state[(size_t)(taps - 1 - (start_row - row)) * channels + c];
+                history[j] = x;
+            }
+            previous_seq = seq;
+        }
+        const float now = in[(size_t)t * in_stride + offset + c];
+        float acc = b;
+#pragma unroll
+        for (int j = 0; j < MAX_TAPS; ++j) {
+            if (j < taps - 1) acc += w[j] * history[j];
+            else if (j == taps - 1) acc += w[j] * now;
+        }
+#pragma unroll
+        for (int j = 0; j < MAX_TAPS - 1; ++j) {
+            if (j < taps - 2) history[j] = history[j + 1];
+            else if (j == taps - 2) history[j] = now;
+        }
+        out[(size_t)t * channels + c] = acc / (1.0f + expf(-acc));
     }
 }
 
@@ -85,10 +111,19 @@ MRS_EXPORT int mrs_causal_conv_silu(const float* in, int in_stride, int offset, 
     if (tokens <= 0) return 0;
     if (channels <= 0 || taps <= 0 || taps > SSM_MAX_TAPS) return MRS_BAD_ARGUMENT;
     const int threads = 128;
-    int per_row = (channels + threads - 1) / threads;
-    if (per_row > 64) per_row = 64;
-    MRS_LAUNCH(causal_conv_silu_kernel, dim3(tokens, per_row), threads, 0, stream, in, in_stride, offset, weight, bias,
-               (const float*)conv_state, state_stride, positions, seq_of_token, q_start, state_slots, out, channels, taps);
+    const int across = (channels + threads - 1) / threads;
+    int per_row = across > 64 ? 64 : across;               // the state update strides over the channels
+    if (across > 65535) return MRS_BAD_ARGUMENT;
+    const dim3 grid((tokens + SSM_CONV_ROWS - 1) / SSM_CONV_ROWS, across);
+    if (taps <= 4)
+        MRS_LAUNCH(causal_conv_silu_kernel<4>, grid, threads, 0, stream, in, in_stride, offset, weight, bias, (const float*)conv_state,
+                   state_stride, positions, seq_of_token, q_start, state_slots, out, tokens, channels, taps);
+    else if (taps <= 8)
+        MRS_LAUNCH(causal_conv_silu_kernel<8>, grid, threads, 0, stream, in, in_stride, offset, weight, bias, (const float*)conv_state,
+                   state_stride, positions, seq_of_token, q_start, state_slots, out, tokens, channels, taps);
+    else
+        MRS_LAUNCH(causal_conv_silu_kernel<SSM_MAX_TAPS>, grid, threads, 0, stream, in, in_stride, offset, weight, bias,
+                   (const float*)conv_state, state_stride, positions, seq_of_token, q_start, state_slots, out, tokens, channels, taps);
     if (update_state && taps > 1)
         MRS_LAUNCH(conv_state_update_kernel, dim3(sequences, per_row), threads, 0, stream, in, in_stride, offset, conv_state,
                    state_stride, positions, q_start, state_slots, channels, taps);
