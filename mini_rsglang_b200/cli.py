@@ -86,14 +86,30 @@ def load_engine(args, limits: RuntimeConfig):
     """The engine of the command line: weights from the model folder, or, with --random-weights, seeded random ones
     for the folder's config.json, drawn on the device."""
     from .engine.handle import EngineHandle
+    from .models.registry import load_config, model_spec_for
 
+    config = load_config(args.model)
+    if limits.prefix_cache and not shares_prefixes(model_spec_for(config)):
+        print("prefix sharing is off: this model keeps a window of keys or a state of its own per request", file=sys.stderr)
+        limits.prefix_cache = False
     if args.random_weights is None:
         return EngineHandle.load(args.model, args.device, args.kv_mib * 1024 * 1024, limits, dtype=args.dtype,
                                  num_pages=args.num_pages)
-    from .models.registry import load_config
-
-    return EngineHandle.from_random(load_config(args.model), args.random_weights, args.device, args.kv_mib * 1024 * 1024,
+    return EngineHandle.from_random(config, args.random_weights, args.device, args.kv_mib * 1024 * 1024,
                                     limits, dtype=args.dtype, num_pages=args.num_pages)
+
+
+def shares_prefixes(spec) -> bool:
+    """Whether requests of this model can read one another's pages: every mixer keeps all its keys and no state."""
+    _, blocks, _, _ = spec.build_parts()
+    for block in blocks:
+        part = block.cache_part()
+        if part is None:
+            continue
+        need = part.cache_need()
+        if part.state_need() is not None or (need is not None and need.kind != "full"):
+            return False
+    return True
 
 
 def event_json(event) -> str:
