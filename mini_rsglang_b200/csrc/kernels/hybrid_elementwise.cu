@@ -34,9 +34,20 @@ __global__ void postnorm_add_norm_kernel(float* __restrict__ stream, const float
     for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_float<T>(res[i] * scale_v * w_next[i]);
 }
 
-// The same with the row kept in registers between the passes (width at most NORM_KEEP * blockDim.x): every element is
-// read once.  A thread takes the elements threadIdx.x, threadIdx.x + blockDim.x, ... in that order, as the kernel above does.
-#define NORM_KEEP 8
+// The same with the row kept in registers between the passes and four elements a load: width a multiple of 4, at most
+// 16 * blockDim.x, rows on 16-byte boundaries.  Every element is read once.
+#define NORM_KEEP 4
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <typename T> __device__ __forceinline__ void st4(T* p, float4 v);
+template <> __device__ __forceinline__ void st4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void st4<bf16>(bf16* p, float4 v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<uint32_t*>(&lo);
+    raw.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
 template <typename T>
 __global__ void postnorm_add_norm_kept_kernel(float* __restrict__ stream, const float* __restrict__ branch,
                                               const float* __restrict__ w_post, const float* __restrict__ w_next, float eps_post,
@@ -47,43 +58,47 @@ __global__ void postnorm_add_norm_kept_kernel(float* __restrict__ stream, const 
     const size_t r = blockIdx.x;
     float* res = stream + r * width;
     const float* a = branch + r * width;
-    float av[NORM_KEEP], rv[NORM_KEEP], wv[NORM_KEEP];
+    const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float4 av[NORM_KEEP], rv[NORM_KEEP], wv[NORM_KEEP];
     float sum = 0.0f;
 #pragma unroll
     for (int j = 0; j < NORM_KEEP; ++j) {
-        const int i = threadIdx.x + j * blockDim.x;
-        av[j] = i < width ? a[i] : 0.0f;
-        sum += av[j] * av[j];
+        const int i = (threadIdx.x + j * blockDim.x) * 4;
+        av[j] = i < width ? ld4(a + i) : zero;
+        sum += av[j].x * av[j].x + av[j].y * av[j].y + av[j].z * av[j].z + av[j].w * av[j].w;
     }
 #pragma unroll
     for (int j = 0; j < NORM_KEEP; ++j) {                  // asked for before the block waits for its sum
-        const int i = threadIdx.x + j * blockDim.x;
-        rv[j] = i < width ? res[i] : 0.0f;
-        wv[j] = i < width ? w_post[i] : 0.0f;
+        const int i = (threadIdx.x + j * blockDim.x) * 4;
+        rv[j] = i < width ? ld4(res + i) : zero;
+        wv[j] = i < width ? ld4(w_post + i) : zero;
     }
     const float scale_a = 1.0f / sqrtf(block_sum(sum, scratch) / (float)width + eps_post);
     sum = 0.0f;
 #pragma unroll
     for (int j = 0; j < NORM_KEEP; ++j) {
-        const int i = threadIdx.x + j * blockDim.x;
+        const int i = (threadIdx.x + j * blockDim.x) * 4;
         if (i < width) {
-            rv[j] = rv[j] + av[j] * scale_a * wv[j];
-            res[i] = rv[j];
-            sum += rv[j] * rv[j];
+            rv[j].x += av[j].x * scale_a * wv[j].x, rv[j].y += av[j].y * scale_a * wv[j].y;
+            rv[j].z += av[j].z * scale_a * wv[j].z, rv[j].w += av[j].w * scale_a * wv[j].w;
+            st4<float>(res + i, rv[j]);
+            sum += rv[j].x * rv[j].x + rv[j].y * rv[j].y + rv[j].z * rv[j].z + rv[j].w * rv[j].w;
         }
     }
     if (w_next == nullptr) return;
 #pragma unroll
     for (int j = 0; j < NORM_KEEP; ++j) {
-        const int i = threadIdx.x + j * blockDim.x;
-        wv[j] = i < width ? w_next[i] : 0.0f;
+        const int i = (threadIdx.x + j * blockDim.x) * 4;
+        wv[j] = i < width ? ld4(w_next + i) : zero;
     }
     const float scale_v = 1.0f / sqrtf(block_sum(sum, scratch) / (float)width + eps_next);
     T* o = out + r * width;
 #pragma unroll
     for (int j = 0; j < NORM_KEEP; ++j) {
-        const int i = threadIdx.x + j * blockDim.x;
-        if (i < width) o[i] = from_float<T>(rv[j] * scale_v * wv[j]);
+        const int i = (threadIdx.x + j * blockDim.x) * 4;
+        if (i < width)
+            st4<T>(o + i, make_float4(rv[j].x * scale_v * wv[j].x, rv[j].y * scale_v * wv[j].y, rv[j].z * scale_v * wv[j].z,
+                                      rv[j].w * scale_v * wv[j].w));
     }
 }
 
@@ -92,11 +107,14 @@ MRS_EXPORT int mrs_postnorm_add_norm(int is_bf16, float* stream, const float* br
     if (rows <= 0) return 0;
     if (width <= 0) return MRS_BAD_ARGUMENT;
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-    if (width <= NORM_KEEP * threads) {
+    const bool aligned = (((uintptr_t)stream | (uintptr_t)branch | (uintptr_t)w_post | (uintptr_t)w_next | (uintptr_t)out) & 15) == 0;
+    if (width % 4 == 0 && aligned && width <= 4 * NORM_KEEP * 512) {
+        int kept_threads = ((width / 4 + NORM_KEEP - 1) / NORM_KEEP + 31) / 32 * 32;      // the row fits the block's registers
+        if (kept_threads < 64) kept_threads = 64;
         if (is_bf16)
-            MRS_LAUNCH(postnorm_add_norm_kept_kernel<bf16>, rows, threads, 0, s, stream, branch, w_post, w_next, eps_post, eps_next, (bf16*)out, width);
+            MRS_LAUNCH(postnorm_add_norm_kept_kernel<bf16>, rows, kept_threads, 0, s, stream, branch, w_post, w_next, eps_post, eps_next, (bf16*)out, width);
         else
-            MRS_LAUNCH(postnorm_add_norm_kept_kernel<float>, rows, threads, 0, s, stream, branch, w_post, w_next, eps_post, eps_next, (float*)out, width);
+            MRS_LAUNCH(postnorm_add_norm_kept_kernel<float>, rows, kept_threads, 0, s, stream, branch, w_post, w_next, eps_post, eps_next, (float*)out, width);
         MRS_RETURN_LAUNCH_STATUS();
     }
     if (is_bf16)
