@@ -25,12 +25,12 @@ __global__ void causal_conv_silu_kernel(const float* __restrict__ in, int in_str
                                         const float* __restrict__ bias, const float* __restrict__ conv_state, long long state_stride,
                                         const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                                         const int* __restrict__ q_start, const int* __restrict__ state_slots,
-                                        float* __restrict__ out, int tokens, int channels, int taps) {
+                                        float* __restrict__ out, int tokens, int channels, int taps, int rows) {
     pdl_launch_dependents();
     pdl_wait();
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= channels) return;
-    const int first = blockIdx.x * SSM_CONV_ROWS, last = min(tokens, first + SSM_CONV_ROWS);
+    const int first = blockIdx.x * rows, last = min(tokens, first + rows);
     float w[MAX_TAPS], history[MAX_TAPS];          // history[j]: the input taps - 1 - j rows back, j < taps - 1
 #pragma unroll
     for (int k = 0; k < MAX_TAPS; ++k) w[k] = k < taps ? weight[(size_t)c * taps + k] : 0.0f;
@@ -114,16 +114,17 @@ MRS_EXPORT int mrs_causal_conv_silu(const float* in, int in_stride, int offset, 
     const int across = (channels + threads - 1) / threads;
     int per_row = across > 64 ? 64 : across;               // the state update strides over the channels
     if (across > 65535) return MRS_BAD_ARGUMENT;
-    const dim3 grid((tokens + SSM_CONV_ROWS - 1) / SSM_CONV_ROWS, across);
+    const int rows = tokens >= 32 * SSM_CONV_ROWS ? SSM_CONV_ROWS : 1;      // few rows (decoded tokens): a thread a row
+    const dim3 grid((tokens + rows - 1) / rows, across);
     if (taps <= 4)
         MRS_LAUNCH(causal_conv_silu_kernel<4>, grid, threads, 0, stream, in, in_stride, offset, weight, bias, (const float*)conv_state,
-                   state_stride, positions, seq_of_token, q_start, state_slots, out, tokens, channels, taps);
+                   state_stride, positions, seq_of_token, q_start, state_slots, out, tokens, channels, taps, rows);
     else if (taps <= 8)
         MRS_LAUNCH(causal_conv_silu_kernel<8>, grid, threads, 0, stream, in, in_stride, offset, weight, bias, (const float*)conv_state,
-                   state_stride, positions, seq_of_token, q_start, state_slots, out, tokens, channels, taps);
+                   state_stride, positions, seq_of_token, q_start, state_slots, out, tokens, channels, taps, rows);
     else
         MRS_LAUNCH(causal_conv_silu_kernel<SSM_MAX_TAPS>, grid, threads, 0, stream, in, in_stride, offset, weight, bias,
-                   (const float*)conv_state, state_stride, positions, seq_of_token, q_start, state_slots, out, tokens, channels, taps);
+                   (const float*)conv_state, state_stride, positions, seq_of_token, q_start, state_slots, out, tokens, channels, taps, rows);
     if (update_state && taps > 1)
         MRS_LAUNCH(conv_state_update_kernel, dim3(sequences, per_row), threads, 0, stream, in, in_stride, offset, conv_state,
                    state_stride, positions, q_start, state_slots, channels, taps);
