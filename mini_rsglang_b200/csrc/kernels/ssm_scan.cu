@@ -161,16 +161,17 @@ __device__ __forceinline__ void cp_async_f1(float* to, const float* from) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(to)), "l"(from));
 }
 
-template <int MODE>
+template <int MODE, int LANES>
 __global__ void ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt_in, int dt_stride,
                                 const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
                                 float* __restrict__ ssm_state, long long state_stride, const int* __restrict__ positions,
                                 const int* __restrict__ q_start, const int* __restrict__ state_slots, float* __restrict__ y,
-                                int heads, int groups, int N, int P, int lanes_per_column, int per, int write_state,
+                                int heads, int groups, int N, int P, int per, int write_state,
                                 float* __restrict__ chunk_state, float* __restrict__ chunk_decay, int chunk_len, int max_chunks,
                                 int slices, int columns, int batch) {
     pdl_launch_dependents();
     pdl_wait();
+    constexpr int lanes_per_column = LANES;                          // lanes that share a column of S (a power of two)
     extern __shared__ __align__(16) float ssm_smem[];
     const int seq = blockIdx.x, head = blockIdx.y / slices, slice = blockIdx.y % slices, chunk = blockIdx.z;
     const int seq_start = q_start[seq], seq_end = q_start[seq + 1];
@@ -289,6 +290,7 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, const float* __re
         const float* b_from = b_rows + (size_t)buffer * batch * padded;
         const float* c_from = c_rows + (size_t)buffer * batch * padded;
         const float* x_from = x_rows + (size_t)buffer * batch * columns;
+        float* y_row = y + (size_t)first * inner + head * P + p;
         for (int t = 0; t < count; ++t) {
             const float decay = decay_rows[buffer * batch + t], dt = dt_rows[buffer * batch + t];
             float x[SSM_COLUMNS], dx[SSM_COLUMNS], sum[SSM_COLUMNS];
@@ -317,9 +319,11 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, const float* __re
             if (MODE != SSM_LOCAL) {
 #pragma unroll
                 for (int j = 0; j < SSM_COLUMNS; ++j) {
+#pragma unroll
                     for (int o = 1; o < lanes_per_column; o <<= 1) sum[j] += __shfl_xor_sync(0xffffffffu, sum[j], o);
-                    if (live[j] && s == 0) y[(size_t)(first + t) * inner + head * P + p + j] = sum[j] + skip * x[j];
+                    if (live[j] && s == 0) y_row[j] = sum[j] + skip * x[j];
                 }
+                y_row += inner;
             }
         }
         step_sizes(buffer ^ 1, next_count, next_raw);
@@ -389,26 +393,33 @@ MRS_EXPORT int mrs_ssm_scan(const float* xbc, const float* dt_in, int dt_stride,
     if (batch > threads) batch = threads;
     if (batch < 1) batch = 1;
     const size_t smem = (size_t)2 * batch * row_floats * sizeof(float);
+#define SSM_LAUNCH(MODE, LANES, GRID, STATE, DECAY, CHUNK, CHUNKS)                                                            \
+    MRS_LAUNCH((ssm_scan_kernel<MODE, LANES>), GRID, threads, smem, stream, xbc, dt_in, dt_stride, dt_bias, a_log, d_skip,         \
+               ssm_state, state_stride, positions, q_start, state_slots, y, heads, groups, N, P, per, write_state, STATE, DECAY,   \
+               CHUNK, CHUNKS, slices, columns, batch)
+#define SSM_LAUNCH_LANES(MODE, GRID, STATE, DECAY, CHUNK, CHUNKS)                                                                \
+    switch (lanes) {                                                                                                               \
+        case 1: SSM_LAUNCH(MODE, 1, GRID, STATE, DECAY, CHUNK, CHUNKS); break;                                                     \
+        case 2: SSM_LAUNCH(MODE, 2, GRID, STATE, DECAY, CHUNK, CHUNKS); break;                                                     \
+        case 4: SSM_LAUNCH(MODE, 4, GRID, STATE, DECAY, CHUNK, CHUNKS); break;                                                     \
+        case 8: SSM_LAUNCH(MODE, 8, GRID, STATE, DECAY, CHUNK, CHUNKS); break;                                                     \
+        case 16: SSM_LAUNCH(MODE, 16, GRID, STATE, DECAY, CHUNK, CHUNKS); break;                                                   \
+        default: SSM_LAUNCH(MODE, 32, GRID, STATE, DECAY, CHUNK, CHUNKS); break;                                                   \
+    }
     if (chunk_len == 0) {
-        MRS_LAUNCH(ssm_scan_kernel<SSM_WHOLE>, dim3(sequences, heads * slices), threads, smem, stream, xbc, dt_in, dt_stride, dt_bias, a_log, d_skip,
-                   ssm_state, state_stride, positions, q_start, state_slots, y, heads, groups, N, P, lanes, per, write_state,
-                   (float*)nullptr, (float*)nullptr, 0, 0, slices, columns, batch);
+        SSM_LAUNCH_LANES(SSM_WHOLE, dim3(sequences, heads * slices), (float*)nullptr, (float*)nullptr, 0, 0);
         MRS_RETURN_LAUNCH_STATUS();
     }
     const int max_chunks = (tokens + chunk_len - 1) / chunk_len;
     if (max_chunks > 65535) return MRS_BAD_ARGUMENT;
     float* chunk_state = scratch;
     float* chunk_decay = scratch + (size_t)sequences * heads * max_chunks * N * P;
-    MRS_LAUNCH(ssm_scan_kernel<SSM_LOCAL>, dim3(sequences, heads * slices, max_chunks), threads, smem, stream, xbc, dt_in, dt_stride, dt_bias, a_log,
-               d_skip, ssm_state, state_stride, positions, q_start, state_slots, y, heads, groups, N, P, lanes, per, write_state,
-               chunk_state, chunk_decay, chunk_len, max_chunks, slices, columns, batch);
+    SSM_LAUNCH_LANES(SSM_LOCAL, dim3(sequences, heads * slices, max_chunks), chunk_state, chunk_decay, chunk_len, max_chunks);
     const int elements = N * P;
     int element_blocks = (elements + 255) / 256;
     if (element_blocks > 64) element_blocks = 64;
     MRS_LAUNCH(ssm_chunk_states_kernel, dim3(sequences, heads, element_blocks), 256, 0, stream, ssm_state, state_stride, positions, q_start,
                state_slots, chunk_state, (const float*)chunk_decay, heads, elements, chunk_len, max_chunks, write_state);
-    MRS_LAUNCH(ssm_scan_kernel<SSM_FINAL>, dim3(sequences, heads * slices, max_chunks), threads, smem, stream, xbc, dt_in, dt_stride, dt_bias, a_log,
-               d_skip, ssm_state, state_stride, positions, q_start, state_slots, y, heads, groups, N, P, lanes, per, write_state,
-               chunk_state, chunk_decay, chunk_len, max_chunks, slices, columns, batch);
+    SSM_LAUNCH_LANES(SSM_FINAL, dim3(sequences, heads * slices, max_chunks), chunk_state, chunk_decay, chunk_len, max_chunks);
     MRS_RETURN_LAUNCH_STATUS();
 }
