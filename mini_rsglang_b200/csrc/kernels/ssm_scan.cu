@@ -219,7 +219,7 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, const float* __re
         float* c_to = c_rows + (size_t)buffer * batch * padded;
         float* x_to = x_rows + (size_t)buffer * batch * columns;
         if (vectors && blockDim.x % (N / 4) == 0) {
-            // a thread's place in a row is the same in every round: the divisions are done once
+            // a thread's place in a row is the same in every pass of the loop: the divisions are done once
             const int quads = N / 4, n = ((int)threadIdx.x % quads) * 4, step = blockDim.x / quads;
             const int where = ((((n % per) >> 2) * lanes_per_column + n / per) << 2);
             const float* r = xbc + (size_t)first * row_width + inner + group * N + n;
