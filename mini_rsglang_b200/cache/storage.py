@@ -53,7 +53,8 @@ class CacheStorage:
             if need is not None:
                 shape = (groups[g].num_pages, need.kv_heads, runtime.page_size, need.head_dim)
                 entry.k = torch.zeros(shape, dtype=runtime.dtype, device=runtime.device)
-                entry.v = torch.zeros((*shape[:3], need.v_head_dim), dtype=runtime.dtype, device=runtime.device)
+                if need.values:
+                    entry.v = torch.zeros((*shape[:3], need.v_head_dim), dtype=runtime.dtype, device=runtime.device)
             if state is not None:
                 entry.state = torch.zeros((max_slots, *state.shape), dtype=state.dtype, device=runtime.device)
             self.entries.append(entry)

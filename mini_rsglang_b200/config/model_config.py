@@ -305,3 +305,158 @@ class NiduvikConfig(ModelConfig):
         if self.eos_token_id is not None:
             out["eos_token_id"] = self.eos_token_id
         return out
+
+
+@dataclass
+class SatedraConfig(ModelConfig):
+    """Satedra: a decoder of pre-norm layers (layer norms with bias) that each hold a latent attention (keys and values
+    made from one small latent a token, which is what the cache keeps; part of every head rotated with stretched rotary
+    positions; a sliding window; gated heads; a layer may read the cache of an earlier one) and, optionally, a
+    feed-forward: a dense gated unit, or routed experts with identity experts, a corrected choice and a gated shared
+    expert.  The logits are scaled by a constant.  config.json names the design under `architecture`; its keys are read
+    as they stand there:
+
+      vocab, width, norm.eps, logit_scale
+      layers[i].type = "latent_attention"
+      layers[i].mixer.{heads, dim, rot_dim, vdim, kv_rank, scale, mask.size, rot.{base, dims, scaling.{factor, original, fast, slow}}, kv_from}
+      layers[i].mlp = null | {kind: "dense", ff} | {kind: "moe", expert.ff, router.{experts, identity, top, scale}, shared.ff}
+
+    `mask` (no window: every earlier key), `rot.scaling` (plain rotary positions), `kv_from`, `router.identity` and `shared`
+    may be left out.  The design states no longest context and no end-of-sequence token; `max_position_embeddings` and
+    `eos_token_id` are read if a file has them."""
+
+    width: int = 0
+    norm_eps: float = 0.0
+    logit_scale: float = 1.0
+    layers: list = None
+
+    MODEL_TYPES: ClassVar[tuple[str, ...]] = ("satedra",)
+    NO_CONTEXT_LIMIT: ClassVar[int] = 1 << 22
+
+    @classmethod
+    def _mixer(cls, i: int, mixer: dict) -> dict:
+        where = f"layers[{i}].mixer"
+        out = {key: _require(mixer, key, int, where) for key in ("heads", "dim", "rot_dim", "vdim", "kv_rank")}
+        out["scale"] = _require(mixer, "scale", float, where)
+        mask = mixer.get("mask")
+        if mask is not None:
+            if not isinstance(mask, dict):
+                raise InvalidRequest(f"config.json: {where}.mask must be an object")
+            out["mask"] = {"size": _require(mask, "size", int, "window")}
+        rot = mixer.get("rot")
+        if not isinstance(rot, dict):
+            raise InvalidRequest(f"config.json: {where}.rot must be an object")
+        out["rot"] = {"base": _require(rot, "base", float, "rotary base"), "dims": _require(rot, "dims", int, "rotated elements")}
+        scaling = rot.get("scaling")
+        if scaling is not None:
+            if not isinstance(scaling, dict):
+                raise InvalidRequest(f"config.json: {where}.rot.scaling must be an object")
+            out["rot"]["scaling"] = {key: _require(scaling, key, float, f"{where}.rot.scaling") for key in ("factor", "original", "fast", "slow")}
+        if mixer.get("kv_from") is not None:
+            out["kv_from"] = _require(mixer, "kv_from", int, "the layer whose cache is read")
+        return out
+
+    @classmethod
+    def _mlp(cls, i: int, mlp) -> dict | None:
+        if mlp is None:
+            return None
+        where = f"layers[{i}].mlp"
+        if not isinstance(mlp, dict):
+            raise InvalidRequest(f"config.json: {where} must be null or an object")
+        kind = _require(mlp, "kind", str, "feed-forward kind")
+        if kind == "dense":
+            return {"kind": kind, "ff": _require(mlp, "ff", int, "feed-forward width")}
+        if kind != "moe":
+            raise InvalidRequest(f"config.json: {where}.kind {kind!r}; known: dense, moe")
+        expert, router = mlp.get("expert"), mlp.get("router")
+        if not isinstance(expert, dict) or not isinstance(router, dict):
+            raise InvalidRequest(f"config.json: {where} needs the objects `expert` and `router`")
+        out = {"kind": kind, "expert": {"ff": _require(expert, "ff", int, "expert width")},
+               "router": {"experts": _require(router, "experts", int, "experts"), "top": _require(router, "top", int, "choices"),
+                          "scale": _require(router, "scale", float, "weight scale"),
+                          "identity": _require(router, "identity", int, "identity experts") if router.get("identity") is not None else 0}}
+        shared = mlp.get("shared")
+        if shared is not None:
+            if not isinstance(shared, dict):
+                raise InvalidRequest(f"config.json: {where}.shared must be an object")
+            out["shared"] = {"ff": _require(shared, "ff", int, "shared expert width")}
+        return out
+
+    @classmethod
+    def from_dict(cls, raw: dict) -> "SatedraConfig":
+        norm = raw.get("norm")
+        if not isinstance(norm, dict):
+            raise InvalidRequest("config.json: missing key `norm` (an object with `eps`)")
+        layers = raw.get("layers")
+        if not isinstance(layers, list) or not layers:
+            raise InvalidRequest("config.json: `layers` must be a list of layers")
+        read = []
+        for i, layer in enumerate(layers):
+            if not isinstance(layer, dict):
+                raise InvalidRequest(f"config.json: layers[{i}] must be an object")
+            kind = _require(layer, "type", str, f"mixer of layer {i}")
+            if kind != "latent_attention":
+                raise InvalidRequest(f"config.json: layers[{i}].type {kind!r}; known: latent_attention")
+            if not isinstance(layer.get("mixer"), dict):
+                raise InvalidRequest(f"config.json: layers[{i}].mixer must be an object")
+            read.append({"type": kind, "mixer": cls._mixer(i, layer["mixer"]), "mlp": cls._mlp(i, layer.get("mlp"))})
+        cfg = cls(model_type="satedra", architectures=["Satedra"], vocab_size=_require(raw, "vocab", int, "vocabulary"),
+                  max_position_embeddings=int(raw.get("max_position_embeddings") or cls.NO_CONTEXT_LIMIT),
+                  eos_token_id=raw.get("eos_token_id"), width=_require(raw, "width", int, "model width"),
+                  norm_eps=_require(norm, "eps", float, "norm epsilon"),
+                  logit_scale=_require(raw, "logit_scale", float, "logit scale") if raw.get("logit_scale") is not None else 1.0,
+                  layers=read)
+        cfg.validate()
+        return cfg
+
+    def validate(self) -> None:
+        if self.vocab_size <= 0 or self.width <= 0 or self.max_position_embeddings <= 0:
+            raise InvalidRequest("invalid Satedra dimensions: every size must be a positive integer")
+        if not math.isfinite(self.norm_eps) or self.norm_eps <= 0 or not math.isfinite(self.logit_scale):
+            raise InvalidRequest("invalid normalization parameters or logit scale")
+        for i, layer in enumerate(self.layers):
+            m = layer["mixer"]
+            if min(m["heads"], m["dim"], m["vdim"], m["kv_rank"]) <= 0 or m["rot_dim"] < 0 or m["scale"] <= 0:
+                raise InvalidRequest(f"layers[{i}].mixer: sizes and scale must be positive")
+            if "mask" in m and m["mask"]["size"] <= 0:
+                raise InvalidRequest(f"layers[{i}].mixer.mask.size must be positive")
+            rot = m["rot"]
+            if rot["dims"] < 0 or rot["dims"] % 2 or rot["dims"] > m["rot_dim"] or rot["base"] <= 1:
+                raise InvalidRequest(f"layers[{i}].mixer.rot: an even number of elements, at most rot_dim, and a base above 1")
+            if "scaling" in rot and min(rot["scaling"].values()) <= 0:
+                raise InvalidRequest(f"layers[{i}].mixer.rot.scaling: every number must be positive")
+            if "kv_from" in m:
+                j = m["kv_from"]
+                if not 0 <= j < i or "kv_from" in self.layers[j]["mixer"]:
+                    raise InvalidRequest(f"layers[{i}].mixer.kv_from must name an earlier layer that keeps a cache of its own")
+                other = self.layers[j]["mixer"]
+                if (other["kv_rank"], other["rot_dim"], other["rot"]) != (m["kv_rank"], m["rot_dim"], m["rot"]):
+                    raise InvalidRequest(f"layers[{i}]: the layer whose cache is read must have the same latent, rotated part and rotation")
+            mlp = layer["mlp"]
+            if mlp is None:
+                continue
+            if mlp["kind"] == "dense":
+                if mlp["ff"] <= 0:
+                    raise InvalidRequest(f"layers[{i}].mlp.ff must be positive")
+                continue
+            r = mlp["router"]
+            if r["experts"] < 0 or r["identity"] < 0 or not 0 < r["top"] <= r["experts"] + r["identity"] or mlp["expert"]["ff"] <= 0:
+                raise InvalidRequest(f"layers[{i}].mlp: experts, identity experts and choices out of range")
+            if "shared" in mlp and mlp["shared"]["ff"] <= 0:
+                raise InvalidRequest(f"layers[{i}].mlp.shared.ff must be positive")
+        if self.eos_token_id is not None:
+            self.eos_ids()
+
+    def eos_ids(self, folder: str | None = None) -> list[int]:
+        if self.eos_token_id is None and (folder is None or not os.path.exists(os.path.join(folder, "generation_config.json"))):
+            return []                # the design names no end-of-sequence token: generation ends by length
+        return super().eos_ids(folder)
+
+    def to_dict(self) -> dict:
+        out = {"architecture": "Satedra", "vocab": self.vocab_size, "width": self.width, "norm": {"eps": self.norm_eps},
+               "logit_scale": self.logit_scale, "layers": self.layers}
+        if self.max_position_embeddings != self.NO_CONTEXT_LIMIT:
+            out["max_position_embeddings"] = self.max_position_embeddings
+        if self.eos_token_id is not None:
+            out["eos_token_id"] = self.eos_token_id
+        return out

@@ -183,20 +183,35 @@ def kernel_library() -> ctypes.CDLL:
     return _load("kernels", builder)
 
 
-HYBRID_KERNEL_SOURCES = ("hybrid_elementwise.cu", "attention_biased.cu", "ssm_scan.cu")
+HYBRID_KERNEL_SOURCES = ("hybrid_elementwise.cu", "ssm_scan.cu")
+LATENT_KERNEL_SOURCES = ("latent_elementwise.cu", "experts.cu", "experts_mma.cu")
 
 
-def hybrid_kernel_library() -> ctypes.CDLL:
-    """The kernels of layers with biased, windowed attention and of state-space recurrences (every size at run
-    time); compiled when a model first needs one of them."""
+def _kernel_group(key: str, name: str, sources: tuple[str, ...]) -> ctypes.CDLL:
     folder = os.path.join(CSRC, "kernels")
 
     def builder():
-        sources = [os.path.join(folder, f) for f in HYBRID_KERNEL_SOURCES]
         nvcc = _find("nvcc", ("/usr/local/cuda/bin/nvcc",))
-        return _build("mrs_hybrid", sources, [nvcc], NVCC_FLAGS, [], folder)
+        return _build(name, [os.path.join(folder, f) for f in sources], [nvcc], NVCC_FLAGS, [], folder)
 
-    return _load("hybrid", builder)
+    return _load(key, builder)
+
+
+def hybrid_kernel_library() -> ctypes.CDLL:
+    """The kernels of layers with a norm after each branch and of state-space recurrences (every size at run
+    time); compiled when a model first needs one of them."""
+    return _kernel_group("hybrid", "mrs_hybrid", HYBRID_KERNEL_SOURCES)
+
+
+def latent_kernel_library() -> ctypes.CDLL:
+    """The kernels of layer norms with bias, latent attention and routed experts (every size at run time); compiled
+    when a model first needs one of them."""
+    return _kernel_group("latent", "mrs_latent", LATENT_KERNEL_SOURCES)
+
+
+def biased_attention_library() -> ctypes.CDLL:
+    """The CUDA-core attention with extras around its scores (every size at run time); compiled at first use."""
+    return _kernel_group("attention_biased", "mrs_attention_biased", ("attention_biased.cu",))
 
 
 def specialised_kernel_library(source: str, defines: dict[str, int], extra_flags: tuple[str, ...] = ()) -> ctypes.CDLL:
@@ -223,6 +238,6 @@ SPECIALISED_BUILDS = tuple((lambda d=d: specialised_kernel_library("attention_mm
     tuple((lambda d=d: specialised_kernel_library("attention_decode_tma.cu", {"MRS_HEAD_DIM": d})) for d in (64, 128)) + \
     tuple((lambda d=d: specialised_kernel_library("attention_prefill_tc.cu", {"MRS_HEAD_DIM": d})) for d in (64, 128)) + \
     (lambda: specialised_kernel_library("gemm_tc.cu", {}), lambda: specialised_kernel_library("gemm_many_rows.cu", {}),
-     hybrid_kernel_library,
+     hybrid_kernel_library, latent_kernel_library, biased_attention_library,
      lambda: specialised_kernel_library("attention_biased_mma.cu", {"MRS_HEAD_DIM": 128, "MRS_VALUE_DIM": 128}),
      lambda: specialised_kernel_library("attention_biased_mma.cu", {"MRS_HEAD_DIM": 64, "MRS_VALUE_DIM": 32}))

@@ -5,18 +5,21 @@
 //   softmax with a sink: p_j = exp(s_j) / (1 + sum exp(s_j))    (sink != 0), else the usual one;
 //   out = (sum p_j v_j) * gate[token, head]                     (gate float32, may be null).
 // Keys have d elements a head and values e (the two need not agree).  Scores, softmax and sums are float32.
-// This is the CUDA-core version: float32 or bfloat16 storage, any sizes up to 256; it is the attention of
-// the 32-bit path and the device-side reference of the tensor-core version.
+// Without value pages the values are the first e elements of the key rows (a latent that serves as key and as
+// value: the cache holds one row a token).  A key on a page that was given back (-1 in the table) counts as unseen.
+// This is the CUDA-core version: float32 or bfloat16 storage, keys of up to 640 and values of up to 512 elements; it is
+// the attention of the 32-bit path and the device-side reference of the tensor-core version.
 //
 // One warp per (token, query head).  The keys a query sees are up to two runs of positions, the kept first
 // ones and the window; the warp walks them as one list, 32 at a time: lane j scores key j with a full dot
 // product, the warp reduces once per tile (online softmax), then all lanes add the 32 weighted value rows.
 #include "common.cuh"
 
-#define ATTN_MAX_D 256
+#define ATTN_MAX_D 640
+#define ATTN_MAX_E 512
 #define ATTN_WARPS 4
 
-template <typename T>
+template <typename T, int EREGS>
 __global__ void attention_biased_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                                              const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                                              const int* __restrict__ block_table, const float* __restrict__ bias,
@@ -41,17 +44,19 @@ __global__ void attention_biased_simt_kernel(const T* __restrict__ q, const T* _
     for (int x = lane; x < d; x += 32) q_s[warp][x] = to_float(q_row[x]);
     __syncwarp();
 
-    float acc[ATTN_MAX_D / 32];
+    const int v_stride = v_cache ? e : d;             // no value pages: a value is the head of its key row
+    const T* values = v_cache ? v_cache : k_cache;
+    float acc[EREGS];
 #pragma unroll
-    for (int i = 0; i < ATTN_MAX_D / 32; ++i) acc[i] = 0.0f;
+    for (int i = 0; i < EREGS; ++i) acc[i] = 0.0f;
     float running_max = sink ? 0.0f : -CUDART_INF_F, running_sum = sink ? 1.0f : 0.0f;
 
     for (int base = 0; base < seen; base += 32) {
         const int u = base + lane;
         const int p = u < kept ? u : first + (u - kept);
         float score = -CUDART_INF_F;
-        if (u < seen) {
-            const int page = pages[p / page_size];
+        const int page = u < seen ? pages[p / page_size] : -1;
+        if (page >= 0) {
             const T* k_row = k_cache + (((size_t)page * nkv + g) * page_size + (p % page_size)) * d;
             float dot = 0.0f;
             for (int x = 0; x < d; ++x) dot += q_s[warp][x] * to_float(k_row[x]);
@@ -61,20 +66,21 @@ __global__ void attention_biased_simt_kernel(const T* __restrict__ q, const T* _
         }
         const float new_max = fmaxf(running_max, warp_max(score));
         const float alpha = new_max == -CUDART_INF_F ? 1.0f : expf(running_max - new_max);
-        const float prob = u < seen ? expf(score - new_max) : 0.0f;
+        const float prob = page >= 0 ? expf(score - new_max) : 0.0f;
         running_sum = running_sum * alpha + warp_sum(prob);
         running_max = new_max;
 #pragma unroll
-        for (int i = 0; i < ATTN_MAX_D / 32; ++i) acc[i] *= alpha;
+        for (int i = 0; i < EREGS; ++i) acc[i] *= alpha;
         const int in_tile = min(32, seen - base);
         for (int j = 0; j < in_tile; ++j) {
             const float pj = __shfl_sync(0xffffffffu, prob, j);
             const int uj = base + j;
             const int pj_pos = uj < kept ? uj : first + (uj - kept);
             const int page = pages[pj_pos / page_size];
-            const T* v_row = v_cache + (((size_t)page * nkv + g) * page_size + (pj_pos % page_size)) * e;
+            if (page < 0) continue;
+            const T* v_row = values + (((size_t)page * nkv + g) * page_size + (pj_pos % page_size)) * v_stride;
 #pragma unroll
-            for (int i = 0; i < ATTN_MAX_D / 32; ++i) {
+            for (int i = 0; i < EREGS; ++i) {
                 const int x = lane + 32 * i;
                 if (x < e) acc[i] += pj * to_float(v_row[x]);
             }
@@ -83,7 +89,7 @@ __global__ void attention_biased_simt_kernel(const T* __restrict__ q, const T* _
     T* o = out + ((size_t)t * nq + h) * e;
     const float factor = (running_sum > 0.0f ? 1.0f / running_sum : 0.0f) * (gate ? gate[(size_t)t * nq + h] : 1.0f);
 #pragma unroll
-    for (int i = 0; i < ATTN_MAX_D / 32; ++i) {
+    for (int i = 0; i < EREGS; ++i) {
         const int x = lane + 32 * i;
         if (x < e) o[x] = from_float<T>(acc[i] * factor);
     }
@@ -94,18 +100,20 @@ MRS_EXPORT int mrs_attention_biased_simt(int is_bf16, const void* q, const void*
                                          void* out, int tokens, int nq, int nkv, int d, int e, int page_size, int table_width,
                                          float scale, float cap, int window, int keep_first, int bias_rows, int sink, void* stream) {
     if (tokens <= 0) return 0;
-    if (d <= 0 || d > ATTN_MAX_D || e <= 0 || e > ATTN_MAX_D || nkv <= 0 || nq % nkv || (bias && bias_rows <= 0) || window < 0 ||
+    if (d <= 0 || d > ATTN_MAX_D || e <= 0 || e > ATTN_MAX_E || (!v_cache && e > d) || nkv <= 0 || nq % nkv || (bias && bias_rows <= 0) || window < 0 ||
         keep_first < 0)
         return MRS_BAD_ARGUMENT;
     const long long units = (long long)tokens * nq;
     const unsigned blocks = (unsigned)((units + ATTN_WARPS - 1) / ATTN_WARPS);
-    if (is_bf16)
-        MRS_LAUNCH(attention_biased_simt_kernel<bf16>, blocks, 32 * ATTN_WARPS, 0, stream, (const bf16*)q, (const bf16*)k_cache,
-                   (const bf16*)v_cache, positions, seq_of_token, block_table, bias, gate, (bf16*)out, tokens, nq, nkv, d, e,
-                   page_size, table_width, scale, cap, window, keep_first, bias_rows, sink);
-    else
-        MRS_LAUNCH(attention_biased_simt_kernel<float>, blocks, 32 * ATTN_WARPS, 0, stream, (const float*)q, (const float*)k_cache,
-                   (const float*)v_cache, positions, seq_of_token, block_table, bias, gate, (float*)out, tokens, nq, nkv, d, e,
-                   page_size, table_width, scale, cap, window, keep_first, bias_rows, sink);
+#define MRS_BIASED_SIMT(T, EREGS)                                                                                              \
+    MRS_LAUNCH((attention_biased_simt_kernel<T, EREGS>), blocks, 32 * ATTN_WARPS, 0, stream, (const T*)q, (const T*)k_cache,      \
+               (const T*)v_cache, positions, seq_of_token, block_table, bias, gate, (T*)out, tokens, nq, nkv, d, e, page_size,    \
+               table_width, scale, cap, window, keep_first, bias_rows, sink)
+    if (is_bf16) {
+        if (e <= 128) MRS_BIASED_SIMT(bf16, 4); else if (e <= 256) MRS_BIASED_SIMT(bf16, 8); else MRS_BIASED_SIMT(bf16, 16);
+    } else {
+        if (e <= 128) MRS_BIASED_SIMT(float, 4); else if (e <= 256) MRS_BIASED_SIMT(float, 8); else MRS_BIASED_SIMT(float, 16);
+    }
+#undef MRS_BIASED_SIMT
     MRS_RETURN_LAUNCH_STATUS();
 }

@@ -1,6 +1,8 @@
 // The biased, windowed attention (see attention_biased.cu for the formulas) on the tensor cores: bfloat16 in,
 // float32 scores, softmax and sums; compiled for one pair of head sizes, -DMRS_HEAD_DIM=<keys> -DMRS_VALUE_DIM=<values>,
-// both multiples of 16 up to 256.
+// both multiples of 16, values up to 256.  With -DMRS_VALUES_IN_KEYS=1 there are no value pages: a value is the first
+// MRS_VALUE_DIM elements of its key row (a latent that serves as key and as value), a block of rows is fetched once and
+// read by both products, and key rows may have up to 640 elements.
 //
 // As in attention_mma.cu a *tile* is a run of consecutive tokens of one request whose query rows are the pairs
 // (token, head within the group), so a key is read once for the whole group of query heads:
@@ -19,8 +21,14 @@
 
 namespace {
 
+#ifndef MRS_VALUES_IN_KEYS
+#define MRS_VALUES_IN_KEYS 0
+#endif
 constexpr int D = MRS_HEAD_DIM, E = MRS_VALUE_DIM;
-static_assert(D % 16 == 0 && D >= 16 && D <= 256 && E % 16 == 0 && E >= 16 && E <= 256, "head sizes: multiples of 16 up to 256");
+constexpr bool IN_KEYS = MRS_VALUES_IN_KEYS != 0;
+constexpr int VW = IN_KEYS ? D : E;            // elements of a row of the tile that holds the values
+static_assert(D % 16 == 0 && D >= 16 && D <= (IN_KEYS ? 640 : 256) && E % 16 == 0 && E >= 16 && E <= 256 && (!IN_KEYS || E <= D),
+              "head sizes: multiples of 16, keys up to 256 (640 with the values inside), values up to 256");
 constexpr int THREADS = 128;
 constexpr int ROWS_WIDE = 64, ROWS_NARROW = 16;
 constexpr int KV_WIDE = 32;            // keys a block in rows mode: small blocks leave room for three or four CTAs an SM
@@ -129,7 +137,7 @@ __device__ __forceinline__ void pv_product(float (&o)[E / 8][4], const float (&s
 #pragma unroll
         for (int dt = 0; dt < E / 8; dt += 2) {
             uint32_t b[4];
-            ldmatrix_x4_trans(b, v_tile + tile_offset<E>(key_row0 + kk * 16 + (lane & 15), dt * 8 + (lane >> 4) * 8));
+            ldmatrix_x4_trans(b, v_tile + tile_offset<VW>(key_row0 + kk * 16 + (lane & 15), dt * 8 + (lane >> 4) * 8));
             mma_bf16(o[dt], a, b[0], b[1]);
             mma_bf16(o[dt + 1], a, b[2], b[3]);
         }
@@ -210,7 +218,7 @@ __global__ void __launch_bounds__(THREADS) attention_biased_rows_kernel(
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);
     bf16* k_tiles = q_tile + ROWS_WIDE * D;
-    bf16* v_tiles = k_tiles + 2 * KV_WIDE * D;
+    bf16* v_tiles = IN_KEYS ? k_tiles : k_tiles + 2 * KV_WIDE * D;
     constexpr int NT = KV_WIDE / 8;
 
     const Tile tile = tiles[blockIdx.x];
@@ -245,14 +253,16 @@ __global__ void __launch_bounds__(THREADS) attention_biased_rows_kernel(
 
     if (blocks.count > 0) {
         load_kv_block<KV_WIDE, D>(k_tiles, k_cache, pages, blocks.at(0) * KV_WIDE, key_end, kv_head, nkv, page_size, page_shift);
-        load_kv_block<KV_WIDE, E>(v_tiles, v_cache, pages, blocks.at(0) * KV_WIDE, key_end, kv_head, nkv, page_size, page_shift);
+        if constexpr (!IN_KEYS)
+            load_kv_block<KV_WIDE, E>(v_tiles, v_cache, pages, blocks.at(0) * KV_WIDE, key_end, kv_head, nkv, page_size, page_shift);
     }
     cp_async_commit();
     for (int i = 0; i < blocks.count; ++i) {
         const int stage = i & 1;
         if (i + 1 < blocks.count) {
             load_kv_block<KV_WIDE, D>(k_tiles + (stage ^ 1) * KV_WIDE * D, k_cache, pages, blocks.at(i + 1) * KV_WIDE, key_end, kv_head, nkv, page_size, page_shift);
-            load_kv_block<KV_WIDE, E>(v_tiles + (stage ^ 1) * KV_WIDE * E, v_cache, pages, blocks.at(i + 1) * KV_WIDE, key_end, kv_head, nkv, page_size, page_shift);
+            if constexpr (!IN_KEYS)
+                load_kv_block<KV_WIDE, E>(v_tiles + (stage ^ 1) * KV_WIDE * E, v_cache, pages, blocks.at(i + 1) * KV_WIDE, key_end, kv_head, nkv, page_size, page_shift);
         }
         cp_async_commit();
         cp_async_wait<1>();
@@ -267,7 +277,7 @@ __global__ void __launch_bounds__(THREADS) attention_biased_rows_kernel(
                 for (int e = 0; e < 4; ++e) s[nt][e] = 0.0f;
             qk_product<NT>(s, q_tile, warp * 16, k_tiles + stage * KV_WIDE * D, 0);
             softmax_step<NT>(s, o, row_max, row_sum, row_pos, row_head, key0, key_end, nq, x);
-            pv_product<NT>(o, s, v_tiles + stage * KV_WIDE * E, 0);
+            pv_product<NT>(o, s, v_tiles + stage * KV_WIDE * VW, 0);
         }
         __syncthreads();
     }
@@ -299,7 +309,7 @@ __global__ void __launch_bounds__(THREADS) attention_biased_keys_kernel(
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);
     bf16* k_tiles = q_tile + ROWS_NARROW * D;
-    bf16* v_tiles = k_tiles + 2 * KV_NARROW * D;
+    bf16* v_tiles = IN_KEYS ? k_tiles : k_tiles + 2 * KV_NARROW * D;
     constexpr int NT = 2;
 
     const Tile tile = tiles[blockIdx.x];
@@ -332,14 +342,16 @@ __global__ void __launch_bounds__(THREADS) attention_biased_keys_kernel(
 
     if (block_first < block_last) {
         load_kv_block<KV_NARROW, D>(k_tiles, k_cache, pages, blocks.at(block_first) * KV_NARROW, key_end, kv_head, nkv, page_size, page_shift);
-        load_kv_block<KV_NARROW, E>(v_tiles, v_cache, pages, blocks.at(block_first) * KV_NARROW, key_end, kv_head, nkv, page_size, page_shift);
+        if constexpr (!IN_KEYS)
+            load_kv_block<KV_NARROW, E>(v_tiles, v_cache, pages, blocks.at(block_first) * KV_NARROW, key_end, kv_head, nkv, page_size, page_shift);
     }
     cp_async_commit();
     for (int i = block_first; i < block_last; ++i) {
         const int stage = (i - block_first) & 1;
         if (i + 1 < block_last) {
             load_kv_block<KV_NARROW, D>(k_tiles + (stage ^ 1) * KV_NARROW * D, k_cache, pages, blocks.at(i + 1) * KV_NARROW, key_end, kv_head, nkv, page_size, page_shift);
-            load_kv_block<KV_NARROW, E>(v_tiles + (stage ^ 1) * KV_NARROW * E, v_cache, pages, blocks.at(i + 1) * KV_NARROW, key_end, kv_head, nkv, page_size, page_shift);
+            if constexpr (!IN_KEYS)
+                load_kv_block<KV_NARROW, E>(v_tiles + (stage ^ 1) * KV_NARROW * E, v_cache, pages, blocks.at(i + 1) * KV_NARROW, key_end, kv_head, nkv, page_size, page_shift);
         }
         cp_async_commit();
         cp_async_wait<1>();
@@ -353,7 +365,7 @@ __global__ void __launch_bounds__(THREADS) attention_biased_keys_kernel(
                 for (int e = 0; e < 4; ++e) s[nt][e] = 0.0f;
             qk_product<NT>(s, q_tile, 0, k_tiles + stage * KV_NARROW * D, warp * 16);
             softmax_step<NT>(s, o, row_max, row_sum, row_pos, row_head, key0, key_end, nq, x);
-            pv_product<NT>(o, s, v_tiles + stage * KV_NARROW * E, warp * 16);
+            pv_product<NT>(o, s, v_tiles + stage * KV_NARROW * VW, warp * 16);
         }
         __syncthreads();
     }
@@ -435,8 +447,9 @@ __global__ void __launch_bounds__(THREADS) attention_biased_combine_kernel(
     }
 }
 
-constexpr size_t smem_rows = (size_t)(ROWS_WIDE * D + 2 * KV_WIDE * (D + E)) * sizeof(bf16);
-constexpr size_t smem_keys_tiles = (size_t)(ROWS_NARROW * D + 2 * KV_NARROW * (D + E)) * sizeof(bf16);
+constexpr int KV_ROW = D + (IN_KEYS ? 0 : E);      // elements fetched a key
+constexpr size_t smem_rows = (size_t)(ROWS_WIDE * D + 2 * KV_WIDE * KV_ROW) * sizeof(bf16);
+constexpr size_t smem_keys_tiles = (size_t)(ROWS_NARROW * D + 2 * KV_NARROW * KV_ROW) * sizeof(bf16);
 constexpr size_t smem_keys_merge = (size_t)ROWS_NARROW * D * sizeof(bf16) + (size_t)(4 * ROWS_NARROW * E + 4 * ROWS_NARROW * 2) * sizeof(float);
 constexpr size_t smem_keys = smem_keys_tiles > smem_keys_merge ? smem_keys_tiles : smem_keys_merge;
 
@@ -450,6 +463,7 @@ int page_shift_of(int page_size) {
 
 MRS_EXPORT int mrs_attention_biased_mma_key_dim() { return D; }
 MRS_EXPORT int mrs_attention_biased_mma_value_dim() { return E; }
+MRS_EXPORT int mrs_attention_biased_mma_values_in_keys() { return IN_KEYS ? 1 : 0; }
 
 // narrow != 0: tiles of up to 16 / group tokens (keys mode); else tiles of up to 64 / group tokens (rows mode).
 // Scratch floats of `splits` > 1 CTAs a tile (tiles of 16 rows only).
@@ -463,7 +477,7 @@ MRS_EXPORT int mrs_attention_biased_mma(int narrow, const void* q, const void* k
                                         float scale, float cap, int window, int keep_first, int sink, int splits, float* scratch,
                                         void* stream) {
     if (num_tiles <= 0) return 0;
-    if (splits < 1 || splits > 65535 || (splits > 1 && (!narrow || !scratch))) return MRS_BAD_ARGUMENT;
+    if (splits < 1 || splits > 65535 || (splits > 1 && (!narrow || !scratch)) || (!IN_KEYS && !v_cache)) return MRS_BAD_ARGUMENT;
     const int shift = page_shift_of(page_size);
     if (shift < 0 || nkv <= 0 || nq % nkv || nq / nkv > (narrow ? ROWS_NARROW : ROWS_WIDE) || (bias && bias_rows <= 0) || window < 0 ||
         keep_first < 0)

@@ -1,0 +1,267 @@
+// Routed experts with shapes that do not depend on the routing, so that a step can be recorded and replayed:
+//
+//   moe_route      float32 router logits [tokens, all experts (+ 1 gate of the shared expert)] -> scores by softmax
+//                  (or sigmoid) over all experts, the `top` largest of score + correction (ties: the lower number),
+//                  their weights score / (sum of the chosen scores + 1e-20) * scale, sigmoid of the shared gate
+//   moe_align      the (token, choice) pairs that go to a routed expert, listed expert by expert, every expert's run
+//                  filled up to whole tiles of `tile` rows (-1), and the expert of every tile (-1: unused);
+//                  experts numbered from `routed` on have no weights (they hand their input on) and get no rows
+//   moe_up / moe_down   the two products of the gated unit over those tiles, on the CUDA cores in float32 sums
+//                  (the 32-bit path and every size; the tensor-core version is experts_mma.cu):
+//                  act[row] = silu(W_gate[e] x) * (W_up[e] x),  y[pair] = W_down[e] act[row]
+//   moe_combine    out[token] = sum over its choices of weight * (y[pair] or, for an expert without weights, the
+//                  input itself) + shared gate * shared expert's output
+//
+// A row's result depends on its own pair alone: which other rows share its tile, and the order of a run, do not enter.
+#include "common.cuh"
+
+namespace {
+
+// One warp a token.  Dynamic shared memory: warps * 2 * all floats (scores, choice scores).
+__global__ void moe_route_kernel(const float* __restrict__ logits, int stride, const float* __restrict__ correction,
+                                 int* __restrict__ chosen, float* __restrict__ weights, float* __restrict__ shared_gate, int tokens,
+                                 int all, int top, float scale, int sigmoid_scores, int has_shared) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float route_smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int t = blockIdx.x * warps + warp;
+    if (t >= tokens) return;
+    float* score = route_smem + (size_t)warp * 2 * all;
+    float* choice = score + all;
+    const float* z = logits + (size_t)t * stride;
+    float top_z = -CUDART_INF_F;
+    for (int e = lane; e < all; e += 32) top_z = fmaxf(top_z, z[e]);
+    top_z = warp_max(top_z);
+    float sum = 0.0f;
+    for (int e = lane; e < all; e += 32) {
+        const float s = sigmoid_scores ? 1.0f / (1.0f + expf(-z[e])) : expf(z[e] - top_z);
+        score[e] = s;
+        sum += s;
+    }
+    sum = warp_sum(sum);
+    const float inv = sigmoid_scores ? 1.0f : 1.0f / sum;
+    for (int e = lane; e < all; e += 32) {
+        score[e] *= inv;
+        choice[e] = score[e] + (correction ? correction[e] : 0.0f);
+    }
+    __syncwarp();
+    float picked_sum = 0.0f;
+    for (int k = 0; k < top; ++k) {
+        float best = -CUDART_INF_F;
+        int best_e = 0x7fffffff;
+        for (int e = lane; e < all; e += 32)
+            if (choice[e] > best) best = choice[e], best_e = e;       // strided upward: the lower number wins a tie in a lane
+        for (int o = 16; o > 0; o >>= 1) {
+            const float other = __shfl_xor_sync(0xffffffffu, best, o);
+            const int other_e = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (other > best || (other == best && other_e < best_e)) best = other, best_e = other_e;
+        }
+        if (best_e >= all) best_e = 0;          // fewer finite scores than choices: cannot happen with finite logits
+        const float s = score[best_e];
+        picked_sum += s;
+        if (lane == 0) {
+            chosen[(size_t)t * top + k] = best_e;
+            weights[(size_t)t * top + k] = s;
+            choice[best_e] = -CUDART_INF_F;
+        }
+        __syncwarp();
+    }
+    if (lane < top) weights[(size_t)t * top + lane] = weights[(size_t)t * top + lane] / (picked_sum + 1e-20f) * scale;
+    for (int k = 32 + lane; k < top; k += 32) weights[(size_t)t * top + k] = weights[(size_t)t * top + k] / (picked_sum + 1e-20f) * scale;
+    if (has_shared && lane == 0) shared_gate[t] = 1.0f / (1.0f + expf(-z[all]));
+}
+
+// One block.  Dynamic shared memory: 3 * routed ints (count, first row, filled).
+__global__ void moe_align_kernel(const int* __restrict__ chosen, int pairs, int routed, int tile, int* __restrict__ sorted_rows,
+                                 int* __restrict__ tile_expert, int capacity) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ int align_smem[];
+    int* count = align_smem;
+    int* first = count + routed;
+    int* filled = first + routed;
+    for (int e = threadIdx.x; e < routed; e += blockDim.x) count[e] = 0, filled[e] = 0;
+    for (int i = threadIdx.x; i < capacity; i += blockDim.x) sorted_rows[i] = -1;
+    for (int i = threadIdx.x; i < capacity / tile; i += blockDim.x) tile_expert[i] = -1;
+    __syncthreads();
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const int e = chosen[i];
+        if (e >= 0 && e < routed) atomicAdd(&count[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < routed; ++e) {
+            first[e] = at;
+            at += (count[e] + tile - 1) / tile * tile;
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < routed; e += blockDim.x)
+        for (int i = first[e] / tile; i < (first[e] + count[e] + tile - 1) / tile; ++i) tile_expert[i] = e;
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const int e = chosen[i];
+        if (e >= 0 && e < routed) sorted_rows[first[e] + atomicAdd(&filled[e], 1)] = i;
+    }
+}
+
+constexpr int SIMT_TM = 32, SIMT_TN = 64, SIMT_TK = 32;
+
+// A tile of 32 rows by 64 output columns of one expert, 256 threads, each 2 rows x 4 columns.
+// GATED: the weights hold 2 * n rows an expert (gate rows, then up rows), out[row] = silu(gate) * up, the input row of
+// a listed pair is x[pair / top]; else the input row is x[its place in the list] and out is written at the pair.
+template <typename T, bool GATED>
+__global__ void __launch_bounds__(256) moe_product_simt_kernel(const T* __restrict__ x, const int* __restrict__ sorted_rows,
+                                                               const int* __restrict__ tile_expert, const T* __restrict__ weight,
+                                                               T* __restrict__ out, int n, int k, int top) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int expert = tile_expert[blockIdx.x];
+    if (expert < 0) return;
+    __shared__ float a_s[SIMT_TM][SIMT_TK + 1];
+    __shared__ float b_s[GATED ? 2 : 1][SIMT_TN][SIMT_TK + 1];
+    __shared__ int row_of[SIMT_TM];
+    const int row0 = blockIdx.x * SIMT_TM, col0 = blockIdx.y * SIMT_TN;
+    if (threadIdx.x < SIMT_TM) row_of[threadIdx.x] = sorted_rows[row0 + threadIdx.x];
+    __syncthreads();
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const T* w = weight + (size_t)expert * (GATED ? 2 : 1) * n * k;
+    float acc[GATED ? 2 : 1][2][4] = {};
+    for (int k0 = 0; k0 < k; k0 += SIMT_TK) {
+        for (int idx = threadIdx.x; idx < SIMT_TM * SIMT_TK; idx += 256) {
+            const int r = idx / SIMT_TK, c = idx % SIMT_TK;
+            const int pair = row_of[r];
+            float v = 0.0f;
+            if (pair >= 0 && k0 + c < k) v = to_float(x[(size_t)(GATED ? pair / top : row0 + r) * k + k0 + c]);
+            a_s[r][c] = v;
+        }
+        for (int idx = threadIdx.x; idx < SIMT_TN * SIMT_TK; idx += 256) {
+            const int r = idx / SIMT_TK, c = idx % SIMT_TK;
+            const bool in = col0 + r < n && k0 + c < k;
+            b_s[0][r][c] = in ? to_float(w[(size_t)(col0 + r) * k + k0 + c]) : 0.0f;
+            if (GATED) b_s[1][r][c] = in ? to_float(w[(size_t)(n + col0 + r) * k + k0 + c]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int c = 0; c < SIMT_TK; ++c) {
+            const float a0 = a_s[ty][c], a1 = a_s[ty + 16][c];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float b = b_s[0][tx + 16 * j][c];
+                acc[0][0][j] += a0 * b;
+                acc[0][1][j] += a1 * b;
+                if (GATED) {
+                    const float u = b_s[1][tx + 16 * j][c];
+                    acc[1][0][j] += a0 * u;
+                    acc[1][1][j] += a1 * u;
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = ty + 16 * i;
+        const int pair = row_of[r];
+        if (pair < 0) continue;
+        T* dst = out + (size_t)(GATED ? row0 + r : pair) * n;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int col = col0 + tx + 16 * j;
+            if (col >= n) continue;
+            float v = acc[0][i][j];
+            if (GATED) {
+                const float g = to_float(from_float<T>(v)), u = to_float(from_float<T>(acc[1][i][j]));   // the projections' own rounding
+                v = g / (1.0f + expf(-g)) * u;
+            }
+            dst[col] = from_float<T>(v);
+        }
+    }
+}
+
+// One block a token.
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ y, const T* __restrict__ h, const T* __restrict__ shared_out,
+                                   const int* __restrict__ chosen, const float* __restrict__ weights, const float* __restrict__ shared_gate,
+                                   T* __restrict__ out, int width, int top, int routed) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const float gate = shared_out ? shared_gate[t] : 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = 0.0f;
+        for (int c = 0; c < top; ++c) {
+            const int pair = t * top + c;
+            const float part = chosen[pair] < routed ? to_float(y[(size_t)pair * width + i]) : to_float(h[(size_t)t * width + i]);
+            v += weights[pair] * part;
+        }
+        if (shared_out) v += gate * to_float(shared_out[(size_t)t * width + i]);
+        out[(size_t)t * width + i] = from_float<T>(v);
+    }
+}
+
+}  // namespace
+
+MRS_EXPORT int mrs_moe_simt_tile() { return SIMT_TM; }
+
+MRS_EXPORT int mrs_moe_route(const float* logits, int stride, const float* correction, int* chosen, float* weights, float* shared_gate,
+                             int tokens, int all, int top, float scale, int sigmoid_scores, int has_shared, void* stream) {
+    if (tokens <= 0) return 0;
+    if (all <= 0 || top <= 0 || top > all || stride < all + (has_shared ? 1 : 0) || (has_shared && !shared_gate)) return MRS_BAD_ARGUMENT;
+    int warps = 4;
+    while (warps > 1 && (size_t)warps * 2 * all * sizeof(float) > 40 * 1024) warps >>= 1;
+    const size_t smem = (size_t)warps * 2 * all * sizeof(float);
+    if (smem > 48 * 1024) return MRS_BAD_ARGUMENT;
+    MRS_LAUNCH(moe_route_kernel, (tokens + warps - 1) / warps, 32 * warps, smem, stream, logits, stride, correction, chosen, weights,
+               shared_gate, tokens, all, top, scale, sigmoid_scores, has_shared);
+    MRS_RETURN_LAUNCH_STATUS();
+}
+
+// Rows of the lists for `pairs` pairs over `routed` experts in tiles of `tile` rows.
+MRS_EXPORT long long mrs_moe_capacity(int pairs, int routed, int tile) {
+    const long long most = (long long)pairs + (long long)routed * (tile - 1);
+    return (most + tile - 1) / tile * tile;
+}
+
+MRS_EXPORT int mrs_moe_align(const int* chosen, int pairs, int routed, int tile, int* sorted_rows, int* tile_expert, int capacity,
+                             void* stream) {
+    if (pairs <= 0) return 0;
+    if (routed <= 0 || tile <= 0 || capacity % tile || capacity < mrs_moe_capacity(pairs, routed, tile) || routed > 4096) return MRS_BAD_ARGUMENT;
+    MRS_LAUNCH(moe_align_kernel, 1, 1024, (size_t)3 * routed * sizeof(int), stream, chosen, pairs, routed, tile, sorted_rows, tile_expert,
+               capacity);
+    MRS_RETURN_LAUNCH_STATUS();
+}
+
+// gated != 0: x [tokens, k], weight [experts, 2 n, k], out [capacity, n]; else x [capacity, k], weight [experts, n, k],
+// out [pairs, n].  Lists in tiles of mrs_moe_simt_tile() rows.
+MRS_EXPORT int mrs_moe_product_simt(int is_bf16, int gated, const void* x, const int* sorted_rows, const int* tile_expert,
+                                    const void* weight, void* out, int capacity, int n, int k, int top, void* stream) {
+    if (capacity <= 0) return 0;
+    if (capacity % SIMT_TM || n <= 0 || k <= 0 || top <= 0) return MRS_BAD_ARGUMENT;
+    const dim3 grid(capacity / SIMT_TM, (n + SIMT_TN - 1) / SIMT_TN);
+#define MRS_MOE_SIMT(T, GATED)                                                                                                   \
+    MRS_LAUNCH((moe_product_simt_kernel<T, GATED>), grid, 256, 0, stream, (const T*)x, sorted_rows, tile_expert, (const T*)weight, \
+               (T*)out, n, k, top)
+    if (is_bf16) {
+        if (gated) MRS_MOE_SIMT(bf16, true); else MRS_MOE_SIMT(bf16, false);
+    } else {
+        if (gated) MRS_MOE_SIMT(float, true); else MRS_MOE_SIMT(float, false);
+    }
+#undef MRS_MOE_SIMT
+    MRS_RETURN_LAUNCH_STATUS();
+}
+
+MRS_EXPORT int mrs_moe_combine(int is_bf16, const void* y, const void* h, const void* shared_out, const int* chosen, const float* weights,
+                               const float* shared_gate, void* out, int tokens, int width, int top, int routed, void* stream) {
+    if (tokens <= 0) return 0;
+    if (width <= 0 || top <= 0 || (shared_out && !shared_gate)) return MRS_BAD_ARGUMENT;
+    const int threads = width >= 1024 ? 256 : 128;
+    if (is_bf16)
+        MRS_LAUNCH(moe_combine_kernel<bf16>, tokens, threads, 0, stream, (const bf16*)y, (const bf16*)h, (const bf16*)shared_out, chosen,
+                   weights, shared_gate, (bf16*)out, width, top, routed);
+    else
+        MRS_LAUNCH(moe_combine_kernel<float>, tokens, threads, 0, stream, (const float*)y, (const float*)h, (const float*)shared_out,
+                   chosen, weights, shared_gate, (float*)out, width, top, routed);
+    MRS_RETURN_LAUNCH_STATUS();
+}

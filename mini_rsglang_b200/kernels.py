@@ -1023,7 +1023,6 @@ _HYBRID_SIGNATURES = {
     "mrs_qkv_bias_store": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_int,
                            _c_int, _c_int, _c_float, _c_int, _c_vp],
     "mrs_gated_part_norm": [_c_int, _c_vp, _c_vp, _c_int, _c_vp, _c_float, _c_vp, _c_int, _c_int, _c_int, _c_vp],
-    "mrs_attention_biased_simt": [_c_int] + [_c_vp] * 9 + [_c_int] * 7 + [_c_float, _c_float, _c_int, _c_int, _c_int, _c_int, _c_vp],
     "mrs_causal_conv_silu": [_c_vp, _c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_ll, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int,
                              _c_int, _c_int, _c_int, _c_vp],
     "mrs_ssm_scan": [_c_vp, _c_vp, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_ll, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int,
@@ -1121,31 +1120,55 @@ def gated_part_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, eps:
                                                 float(eps), out.data_ptr(), tokens, inner, int(parts), _stream()), "gated_part_norm")
 
 
+_biased_simt_lib = None
+
+
+def biased_attention_library() -> ctypes.CDLL:
+    global _biased_simt_lib
+    if _biased_simt_lib is None:
+        if not torch.cuda.is_available():
+            raise BackendError("no CUDA device: the engine has no CPU path")
+        from .csrc.build import biased_attention_library as build
+
+        lib = build()
+        lib.mrs_attention_biased_simt.argtypes = [_c_int] + [_c_vp] * 9 + [_c_int] * 7 + [_c_float, _c_float, _c_int, _c_int, _c_int,
+                                                                                         _c_int, _c_vp]
+        lib.mrs_attention_biased_simt.restype = _c_int
+        _biased_simt_lib = lib
+    return _biased_simt_lib
+
+
 def attention_biased_simt(q, k_cache, v_cache, positions, seq_of_token, block_table, out, nq: int, nkv: int, d: int, e: int,
                           scale: float, cap: float = 0.0, window: int = 0, keep_first: int = 0, bias: torch.Tensor | None = None,
                           gate: torch.Tensor | None = None, sink: bool = False) -> None:
     """Causal paged attention with a soft cap on the scores, a bias by distance (`bias` float32 [rows, nq], the last row
     for every larger distance), a window that keeps the first `keep_first` positions, an optional sink in the softmax
-    and an optional gate a (token, head); keys of d and values of e elements.  One warp per (token, head)."""
+    and an optional gate a (token, head); keys of d and values of e elements.  `v_cache` None: the values are the first
+    e elements of the key rows.  One warp per (token, head)."""
     tokens = q.shape[0]
     _need(q, None, "q", (tokens, nq * d))
     _need(k_cache, q.dtype, "key pages")
-    _need(v_cache, q.dtype, "value pages")
     _need(out, q.dtype, "attention out", (tokens, nq * e))
     _need(positions, torch.int32, "positions", (tokens,))
     _need(seq_of_token, torch.int32, "seq_of_token", (tokens,))
     _need(block_table, torch.int32, "block_table")
     page_size = k_cache.shape[2]
-    if tuple(k_cache.shape[1:]) != (nkv, page_size, d) or tuple(v_cache.shape[1:]) != (nkv, page_size, e):
+    if tuple(k_cache.shape[1:]) != (nkv, page_size, d):
         raise InvalidRequest("attention: the pages do not match heads and head sizes")
+    if v_cache is not None:
+        _need(v_cache, q.dtype, "value pages")
+        if tuple(v_cache.shape[1:]) != (nkv, page_size, e):
+            raise InvalidRequest("attention: the pages do not match heads and head sizes")
+    elif e > d:
+        raise InvalidRequest("attention: values inside the key rows cannot be longer than the rows")
     if bias is not None:
         _need(bias, torch.float32, "distance bias")
         if bias.dim() != 2 or bias.shape[1] != nq:
             raise InvalidRequest("attention: the distance bias must be [rows, query heads]")
     if gate is not None:
         _need(gate, torch.float32, "attention gate", (tokens, nq))
-    _check(hybrid_library().mrs_attention_biased_simt(
-        _is_bf16(q.dtype), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), positions.data_ptr(), seq_of_token.data_ptr(),
+    _check(biased_attention_library().mrs_attention_biased_simt(
+        _is_bf16(q.dtype), q.data_ptr(), k_cache.data_ptr(), _ptr(v_cache), positions.data_ptr(), seq_of_token.data_ptr(),
         block_table.data_ptr(), _ptr(bias), _ptr(gate), out.data_ptr(), tokens, nq, nkv, d, e, page_size, block_table.shape[1],
         float(scale), float(cap), int(window), int(keep_first), bias.shape[0] if bias is not None else 0, int(sink), _stream()),
         "attention_biased_simt")
@@ -1237,25 +1260,31 @@ def ssm_chunk_length(tokens: int, sequences: int, heads: int, n_state: int, head
 _biased_mma_libs: dict[tuple, ctypes.CDLL] = {}
 
 
-def attention_biased_mma_supported(d: int, e: int, group: int, page_size: int) -> bool:
-    """Head sizes that are multiples of 16 up to 256, groups of up to 64 query heads, pages of a power of two."""
-    return (d % 16 == 0 and e % 16 == 0 and 16 <= d <= 256 and 16 <= e <= 256 and group <= MMA_ROWS_WIDE
-            and page_size & (page_size - 1) == 0)
+def attention_biased_mma_supported(d: int, e: int, group: int, page_size: int, values_in_keys: bool = False) -> bool:
+    """Head sizes that are multiples of 16 (keys up to 256, or 640 with the values inside their rows; values up to 256),
+    groups of up to 64 query heads, pages of a power of two."""
+    return (d % 16 == 0 and e % 16 == 0 and 16 <= d <= (640 if values_in_keys else 256) and 16 <= e <= 256
+            and (not values_in_keys or e <= d) and group <= MMA_ROWS_WIDE and page_size & (page_size - 1) == 0)
 
 
-def attention_biased_mma_library(d: int, e: int) -> ctypes.CDLL:
-    """The tensor-core biased attention compiled for key heads of `d` and value heads of `e` elements (at first use)."""
-    if (d, e) not in _biased_mma_libs:
+def attention_biased_mma_library(d: int, e: int, values_in_keys: bool = False) -> ctypes.CDLL:
+    """The tensor-core biased attention compiled for key heads of `d` and value heads of `e` elements (at first use);
+    `values_in_keys`: for caches without value pages, whose values are the first `e` elements of the key rows."""
+    key = (d, e, bool(values_in_keys))
+    if key not in _biased_mma_libs:
         if not torch.cuda.is_available():
             raise BackendError("no CUDA device: the engine has no CPU path")
-        lib = specialised_kernel_library("attention_biased_mma.cu", {"MRS_HEAD_DIM": d, "MRS_VALUE_DIM": e})
+        defines = {"MRS_HEAD_DIM": d, "MRS_VALUE_DIM": e}
+        if values_in_keys:
+            defines["MRS_VALUES_IN_KEYS"] = 1
+        lib = specialised_kernel_library("attention_biased_mma.cu", defines)
         lib.mrs_attention_biased_mma.argtypes = [_c_int] + [_c_vp] * 5 + [_c_int, _c_vp, _c_int, _c_vp, _c_vp, _c_int, _c_vp, _c_int,
                                                  _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_int, _c_int, _c_vp, _c_vp]
         lib.mrs_attention_biased_mma.restype = _c_int
         lib.mrs_attention_biased_mma_scratch_floats.argtypes = [_c_int, _c_int, _c_int]
         lib.mrs_attention_biased_mma_scratch_floats.restype = ctypes.c_longlong
-        _biased_mma_libs[(d, e)] = lib
-    return _biased_mma_libs[(d, e)]
+        _biased_mma_libs[key] = lib
+    return _biased_mma_libs[key]
 
 
 def attention_biased_mma(q, k_cache, v_cache, positions, block_table, tiles, out, nq: int, nkv: int, d: int, e: int, scale: float,
@@ -1263,12 +1292,14 @@ def attention_biased_mma(q, k_cache, v_cache, positions, block_table, tiles, out
                          gate: torch.Tensor | None = None, sink: bool = False, narrow: bool = False, splits: int = 1) -> None:
     """`attention_biased_simt`'s formulas on the tensor cores, bfloat16, over a list of tiles (sequence, first row, tokens, 0):
     `narrow` tiles hold up to 16 // (nq // nkv) tokens (decoded tokens, short portions), the others up to 64 // (nq // nkv).
-    `splits` > 1 (narrow tiles): that many CTAs share a tile's key blocks and a second kernel merges them."""
+    `splits` > 1 (narrow tiles): that many CTAs share a tile's key blocks and a second kernel merges them.
+    `v_cache` None: the values are the first `e` elements of the key rows."""
     global launch_count
     tokens = q.shape[0]
     _need(q, torch.bfloat16, "q", (tokens, nq * d))
     _need(k_cache, torch.bfloat16, "key pages")
-    _need(v_cache, torch.bfloat16, "value pages")
+    if v_cache is not None:
+        _need(v_cache, torch.bfloat16, "value pages")
     _need(out, torch.bfloat16, "attention out", (tokens, nq * e))
     _need(positions, torch.int32, "positions", (tokens,))
     _need(block_table, torch.int32, "block_table")
@@ -1276,7 +1307,7 @@ def attention_biased_mma(q, k_cache, v_cache, positions, block_table, tiles, out
     page_size = k_cache.shape[2]
     if tiles.dim() != 2 or tiles.shape[1] != 4:
         raise InvalidRequest("attention tiles must be [n, 4] (sequence, first token, tokens, 0)")
-    if tuple(k_cache.shape[1:]) != (nkv, page_size, d) or tuple(v_cache.shape[1:]) != (nkv, page_size, e):
+    if tuple(k_cache.shape[1:]) != (nkv, page_size, d) or (v_cache is not None and tuple(v_cache.shape[1:]) != (nkv, page_size, e)):
         raise InvalidRequest("attention: the pages do not match heads and head sizes")
     if bias is not None:
         _need(bias, torch.float32, "distance bias")
@@ -1284,16 +1315,225 @@ def attention_biased_mma(q, k_cache, v_cache, positions, block_table, tiles, out
             raise InvalidRequest("attention: the distance bias must be [rows, query heads]")
     if gate is not None:
         _need(gate, torch.float32, "attention gate", (tokens, nq))
-    lib = attention_biased_mma_library(d, e)
+    lib = attention_biased_mma_library(d, e, values_in_keys=v_cache is None)
     scratch = None
     if splits > 1:
         if not narrow:
             raise InvalidRequest("only tiles of 16 rows share their keys among CTAs")
         scratch = attention_scratch(q.device, lib.mrs_attention_biased_mma_scratch_floats(tiles.shape[0], nkv, splits))
         launch_count += 1
-    _check(lib.mrs_attention_biased_mma(int(narrow), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), positions.data_ptr(),
+    _check(lib.mrs_attention_biased_mma(int(narrow), q.data_ptr(), k_cache.data_ptr(), _ptr(v_cache), positions.data_ptr(),
                                         block_table.data_ptr(), block_table.shape[1], tiles.data_ptr(), tiles.shape[0], out.data_ptr(),
                                         _ptr(bias), bias.shape[0] if bias is not None else 0, _ptr(gate), nq, nkv, page_size,
                                         float(scale), float(cap), int(window), int(keep_first), int(sink), int(splits), _ptr(scratch),
                                         _stream()),
            "attention_biased_mma")
+
+
+# ------------------------------------------------------------------------------------------------
+# layer norms with bias, latent attention, routed experts
+# ------------------------------------------------------------------------------------------------
+_LATENT_SIGNATURES = {
+    "mrs_add_layernorm": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_float, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_vp],
+    "mrs_latent_prepare": [_c_int, _c_vp, _c_int, _c_vp, _c_float, _c_vp, _c_float, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp] +
+                          [_c_int] * 8 + [_c_vp],
+    "mrs_scale": [_c_vp, ctypes.c_longlong, _c_float, _c_vp],
+    "mrs_moe_route": [_c_vp, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_vp],
+    "mrs_moe_align": [_c_vp, _c_int, _c_int, _c_int, _c_vp, _c_vp, _c_int, _c_vp],
+    "mrs_moe_product_simt": [_c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_vp],
+    "mrs_moe_product_mma": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_vp],
+    "mrs_moe_combine": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_vp],
+}
+_latent_lib = None
+
+
+def latent_library() -> ctypes.CDLL:
+    global _latent_lib
+    if _latent_lib is None:
+        if not torch.cuda.is_available():
+            raise BackendError("no CUDA device: the engine has no CPU path")
+        from .csrc.build import latent_kernel_library
+
+        lib = latent_kernel_library()
+        for name, argtypes in _LATENT_SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = argtypes
+            fn.restype = _c_int
+        lib.mrs_moe_capacity.argtypes = [_c_int, _c_int, _c_int]
+        lib.mrs_moe_capacity.restype = ctypes.c_longlong
+        for name in ("mrs_moe_simt_tile", "mrs_moe_mma_tile"):
+            getattr(lib, name).argtypes = []
+            getattr(lib, name).restype = _c_int
+        _latent_lib = lib
+    return _latent_lib
+
+
+def add_layernorm(residual: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, bias: torch.Tensor, eps: float,
+                  out: torch.Tensor, rows: torch.Tensor | None = None, write_back: bool = True) -> None:
+    """v = residual (+ delta); residual = v when write_back; out = (v - mean) / sqrt(var + eps) * weight + bias.
+    With `rows`, out[i] comes from source row rows[i]."""
+    n_rows, width = out.shape
+    _need(residual, torch.float32, "add_layernorm residual")
+    _need(weight, torch.float32, "add_layernorm weight", (width,))
+    _need(bias, torch.float32, "add_layernorm bias", (width,))
+    _need(out, None, "add_layernorm out")
+    if residual.shape[1] != width:
+        raise InvalidRequest("add_layernorm: width mismatch")
+    if delta is not None:
+        _need(delta, out.dtype, "add_layernorm delta", tuple(residual.shape))
+    if rows is not None:
+        _need(rows, torch.int32, "add_layernorm rows", (n_rows,))
+    elif residual.shape[0] != n_rows:
+        raise InvalidRequest("add_layernorm: row count mismatch")
+    _check(latent_library().mrs_add_layernorm(_is_bf16(out.dtype), residual.data_ptr(), _ptr(delta), weight.data_ptr(), bias.data_ptr(),
+                                              float(eps), out.data_ptr(), _ptr(rows), n_rows, width, int(write_back), _stream()),
+           "add_layernorm")
+
+
+def scale_(x: torch.Tensor, factor: float) -> None:
+    """x *= factor, float32, in place."""
+    _need(x, torch.float32, "scaled tensor")
+    _check(latent_library().mrs_scale(x.data_ptr(), x.numel(), float(factor), _stream()), "scale")
+
+
+def latent_prepare(proj: torch.Tensor, latent_weight: torch.Tensor | None, eps: float, inv_freq: torch.Tensor | None, magnitude: float,
+                   positions: torch.Tensor, slots: torch.Tensor | None, q_plain: torch.Tensor, q_rows: torch.Tensor,
+                   cache: torch.Tensor | None, gate: torch.Tensor | None, heads: int, plain: int, rotated: int, latent: int,
+                   rotary: int, has_latent: bool) -> None:
+    """After the fused float32 projection q | (latent, rotated key part) | (one gate a head) of a latent attention:
+    `q_plain` [heads, tokens, plain] gets the unrotated query parts, the last `rotated` columns of `q_rows`
+    [tokens, heads, latent + rotated] the rotated ones; with `has_latent`, the latent over its root mean square times
+    `latent_weight` and the rotated key part go into `cache` [pages, 1, page, latent + rotated] at `slots` (None, or a
+    slot of -1: nowhere); `gate` [tokens, heads] float32 gets the sigmoids.  Of a rotated part the first `rotary`
+    elements turn, element i with i + rotary / 2, by position * inv_freq[i], cosines and sines times `magnitude`."""
+    tokens, width = proj.shape
+    _need(proj, torch.float32, "latent projection")
+    _need(q_plain, None, "q_plain", (heads, tokens, plain))
+    _need(q_rows, q_plain.dtype, "q_rows", (tokens, heads, latent + rotated))
+    _need(positions, torch.int32, "positions", (tokens,))
+    if rotary:
+        _need(inv_freq, torch.float32, "rotation frequencies", (rotary // 2,))
+    if has_latent:
+        _need(latent_weight, torch.float32, "latent norm weight", (latent,))
+    if cache is not None:
+        _need(cache, q_plain.dtype, "latent pages")
+        if cache.dim() != 4 or cache.shape[1] != 1 or cache.shape[3] != latent + rotated:
+            raise InvalidRequest("latent_prepare: the pages must be [pages, 1, page, latent + rotated]")
+        _need(slots, torch.int32, "slots", (tokens,))
+    if gate is not None:
+        _need(gate, torch.float32, "gate", (tokens, heads))
+    _check(latent_library().mrs_latent_prepare(
+        _is_bf16(q_plain.dtype), proj.data_ptr(), width, _ptr(latent_weight), float(eps), _ptr(inv_freq), float(magnitude),
+        positions.data_ptr(), _ptr(slots) if cache is not None else None, q_plain.data_ptr(), q_rows.data_ptr(), _ptr(cache), _ptr(gate),
+        tokens, heads, plain, rotated, latent, rotary, int(has_latent), int(gate is not None), _stream()), "latent_prepare")
+
+
+def moe_route(logits: torch.Tensor, correction: torch.Tensor | None, chosen: torch.Tensor, weights: torch.Tensor,
+              shared_gate: torch.Tensor | None, experts: int, top: int, scale: float, sigmoid_scores: bool = False) -> None:
+    """Router logits float32 [tokens, experts (+ 1)] -> `chosen` [tokens, top] int32, the `top` experts with the largest
+    score + correction, and `weights` [tokens, top] float32, score / (sum of the chosen + 1e-20) * scale; scores are
+    the softmax (or the sigmoids) of the first `experts` columns.  With `shared_gate` [tokens] the column after them
+    is one more gate, whose sigmoid it gets."""
+    tokens = logits.shape[0]
+    _need(logits, torch.float32, "router logits", (tokens, experts + (1 if shared_gate is not None else 0)))
+    if correction is not None:
+        _need(correction, torch.float32, "router correction", (experts,))
+    _need(chosen, torch.int32, "chosen experts", (tokens, top))
+    _need(weights, torch.float32, "expert weights", (tokens, top))
+    if shared_gate is not None:
+        _need(shared_gate, torch.float32, "shared gate", (tokens,))
+    _check(latent_library().mrs_moe_route(logits.data_ptr(), logits.shape[1], _ptr(correction), chosen.data_ptr(), weights.data_ptr(),
+                                          _ptr(shared_gate), tokens, experts, top, float(scale), int(sigmoid_scores),
+                                          int(shared_gate is not None), _stream()), "moe_route")
+
+
+def moe_capacity(pairs: int, routed: int, tile: int) -> int:
+    """Rows of the expert lists for `pairs` (token, choice) pairs: every expert's run filled up to whole tiles."""
+    return int(latent_library().mrs_moe_capacity(pairs, routed, tile))
+
+
+def moe_simt_tile() -> int:
+    return int(latent_library().mrs_moe_simt_tile())
+
+
+def moe_mma_tile() -> int:
+    return int(latent_library().mrs_moe_mma_tile())
+
+
+def moe_mma_supported(x: torch.Tensor, inner: int) -> bool:
+    """bfloat16 with rows on 16-byte boundaries in both products: the width and the experts' inner size multiples of 8."""
+    return x.dtype is torch.bfloat16 and x.shape[1] % 8 == 0 and inner % 8 == 0
+
+
+def moe_align(chosen: torch.Tensor, routed: int, tile: int, sorted_rows: torch.Tensor, tile_expert: torch.Tensor) -> None:
+    """Lists the pairs of `chosen` [tokens, top] that name one of the first `routed` experts, expert by expert, every run
+    filled up with -1 to whole tiles: `sorted_rows` [capacity] the pairs (token * top + choice), `tile_expert`
+    [capacity / tile] the expert of every tile (-1: unused)."""
+    _need(chosen, torch.int32, "chosen experts")
+    _need(sorted_rows, torch.int32, "sorted rows")
+    _need(tile_expert, torch.int32, "tile experts", (sorted_rows.shape[0] // tile,))
+    _check(latent_library().mrs_moe_align(chosen.data_ptr(), chosen.numel(), routed, tile, sorted_rows.data_ptr(), tile_expert.data_ptr(),
+                                          sorted_rows.shape[0], _stream()), "moe_align")
+
+
+def moe_product(x: torch.Tensor, sorted_rows: torch.Tensor, tile_expert: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
+                top: int, gated: bool, tensor_cores: bool = False) -> None:
+    """One product of the experts over the lists of `moe_align`, on the CUDA cores (tiles of `moe_simt_tile()` rows) or,
+    with `tensor_cores` (bfloat16, k a multiple of 8), on the tensor cores (tiles of `moe_mma_tile()` rows).
+    `gated`: x [tokens, k], weight [experts, 2 n, k] (gate rows, then up rows), out [capacity, n] = silu(gate) * up of
+    every listed pair's token; else x [capacity, k], weight [experts, n, k], out [pairs, n] written at the pair."""
+    capacity = sorted_rows.shape[0]
+    k = x.shape[1]
+    n = out.shape[1]
+    _need(x, None, "expert input")
+    _need(weight, x.dtype, "expert weights", (weight.shape[0], (2 if gated else 1) * n, k))
+    _need(out, x.dtype, "expert output")
+    if (out.shape[0] if gated else x.shape[0]) != capacity:
+        raise InvalidRequest("moe_product: the listed rows do not match the lists")
+    if tensor_cores:
+        _need(x, torch.bfloat16, "expert input")
+        _check(latent_library().mrs_moe_product_mma(int(gated), x.data_ptr(), sorted_rows.data_ptr(), tile_expert.data_ptr(),
+                                                    weight.data_ptr(), out.data_ptr(), capacity, n, k, top, _stream()), "moe_product_mma")
+        return
+    _check(latent_library().mrs_moe_product_simt(_is_bf16(x.dtype), int(gated), x.data_ptr(), sorted_rows.data_ptr(), tile_expert.data_ptr(),
+                                                 weight.data_ptr(), out.data_ptr(), capacity, n, k, top, _stream()), "moe_product_simt")
+
+
+def moe_experts(h: torch.Tensor, chosen: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, y: torch.Tensor, routed: int,
+                tensor_cores: bool | None = None) -> None:
+    """y[token * top + choice] = W_down[e] (silu(W_gate[e] h) * (W_up[e] h)) for every pair whose expert e = chosen[token,
+    choice] is one of the first `routed`; the other rows of y are left as they are.  `gate_up` [routed, 2 inner, width]
+    (gate rows, then up rows), `down` [routed, width, inner].  `tensor_cores` None: wherever the tensor-core product applies."""
+    tokens, top = chosen.shape
+    inner = down.shape[2]
+    if tensor_cores is None:
+        tensor_cores = moe_mma_supported(h, inner)
+    tile = moe_mma_tile() if tensor_cores else moe_simt_tile()
+    capacity = moe_capacity(tokens * top, routed, tile)
+    sorted_rows = torch.empty((capacity,), dtype=torch.int32, device=h.device)
+    tile_expert = torch.empty((capacity // tile,), dtype=torch.int32, device=h.device)
+    moe_align(chosen, routed, tile, sorted_rows, tile_expert)
+    act = torch.empty((capacity, inner), dtype=h.dtype, device=h.device)
+    moe_product(h, sorted_rows, tile_expert, gate_up, act, top, gated=True, tensor_cores=tensor_cores)
+    moe_product(act, sorted_rows, tile_expert, down, y, top, gated=False, tensor_cores=tensor_cores)
+
+
+def moe_combine(y: torch.Tensor | None, h: torch.Tensor, shared_out: torch.Tensor | None, chosen: torch.Tensor, weights: torch.Tensor,
+                shared_gate: torch.Tensor | None, out: torch.Tensor, routed: int) -> None:
+    """out[token] = sum over its choices of weight * (y[pair] for one of the first `routed` experts, else h[token])
+    (+ shared_gate[token] * shared_out[token])."""
+    tokens, width = h.shape
+    top = chosen.shape[1]
+    _need(h, None, "expert input", (tokens, width))
+    if y is not None:
+        _need(y, h.dtype, "expert outputs", (tokens * top, width))
+    elif routed > 0:
+        raise InvalidRequest("moe_combine: experts with weights need their outputs")
+    _need(out, h.dtype, "combined output", (tokens, width))
+    _need(chosen, torch.int32, "chosen experts", (tokens, top))
+    _need(weights, torch.float32, "expert weights", (tokens, top))
+    if shared_out is not None:
+        _need(shared_out, h.dtype, "shared expert output", (tokens, width))
+        _need(shared_gate, torch.float32, "shared gate", (tokens,))
+    _check(latent_library().mrs_moe_combine(_is_bf16(h.dtype), _ptr(y), h.data_ptr(), _ptr(shared_out), chosen.data_ptr(), weights.data_ptr(),
+                                            _ptr(shared_gate), out.data_ptr(), tokens, width, top, routed, _stream()), "moe_combine")

@@ -68,9 +68,12 @@ class KVNeed:
     window: int = 0
     value_dim: int = 0       # elements of a value head where they differ from a key head's (0: head_dim)
     keep_first: int = 0      # "window": the first positions stay in sight, their pages are kept
+    values: bool = True      # False: no value pages; what serves as value lies in the key rows (a latent)
 
     @property
     def v_head_dim(self) -> int:
+        if not self.values:
+            return 0
         return self.value_dim or self.head_dim
 
 

@@ -27,12 +27,20 @@ def _branch(part, h, stream, norm, *args):
 class PreNormBlock(Block):
     links_norms = True
     roles = {"norm1": NORMS, "mixer": MIXERS, "norm2": NORMS, "feed_forward": FEED_FORWARDS}
+    optional_roles = ("norm2", "feed_forward")       # a layer may be a mixer alone (both are left out together)
     entry_role = "norm1"
+
+    def __init__(self, prefix: str, **parts):
+        super().__init__(prefix, **parts)
+        if (self.norm2 is None) != (self.feed_forward is None):
+            raise InvalidRequest(f"block at {prefix!r}: a feed-forward comes with the norm before it")
 
     def forward(self, stream, pending, ctx, cache, write_cache=True, next_norm=None):
         if observing(ctx):
             return self.forward_observed(stream, pending, ctx, cache, write_cache)
         h = self.norm1.add_norm(stream, pending)
+        if self.feed_forward is None:
+            return _branch(self.mixer, h, stream, next_norm, ctx, cache, write_cache)
         a = _branch(self.mixer, h, stream, self.norm2, ctx, cache, write_cache)
         h = self.norm2.add_norm(stream, a)
         return _branch(self.feed_forward, h, stream, next_norm, ctx)
@@ -43,6 +51,9 @@ class PreNormBlock(Block):
         h = plain(self.norm1.add_norm(stream, pending))
         ctx.observe(f"{ctx.label}-input_norm", h)
         a = self.mixer.forward(h, ctx, cache, write_cache)
+        if self.feed_forward is None:
+            ctx.observe(f"{ctx.label}-output", stream + a.float())
+            return a
         h = plain(self.norm2.add_norm(stream, a))
         f = self.feed_forward.forward(h, ctx)
         ctx.observe(f"{ctx.label}-output", stream + f.float())

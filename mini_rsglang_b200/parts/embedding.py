@@ -33,18 +33,22 @@ class TokenEmbedding(Embedding):
 
 @HEADS.register("linear_head")
 class OutputHead(Head):
-    def __init__(self, prefix: str, vocab: int, width: int, tied_to: str | None = None):
+    def __init__(self, prefix: str, vocab: int, width: int, tied_to: str | None = None, leaf: str = "weight", scale: float = 1.0):
+        """`leaf`: the matrix's name below the part's root ("": the root itself); `scale`: a constant that multiplies the logits."""
         super().__init__(prefix)
-        self.vocab, self.width, self.tied_to = int(vocab), int(width), tied_to
+        self.vocab, self.width, self.tied_to, self.leaf, self.scale = int(vocab), int(width), tied_to, leaf, float(scale)
         self.weight = None
 
     def weight_specs(self):
-        return [] if self.tied_to else [WeightSpec(self.name("weight"), (self.vocab, self.width))]
+        return [] if self.tied_to else [WeightSpec(self.name(self.leaf), (self.vocab, self.width))]
 
     def bind(self, tensors, runtime):
         super().bind(tensors, runtime)
-        self.weight = tensors[self.tied_to if self.tied_to else self.name("weight")]
+        self.weight = tensors[self.tied_to if self.tied_to else self.name(self.leaf)]
 
     def forward(self, hidden) -> torch.Tensor:
         """`hidden`: the normalised rows, or a `Prenormed` that the product finishes."""
-        return linear(hidden, self.weight, out_dtype=torch.float32)
+        logits = linear(hidden, self.weight, out_dtype=torch.float32)
+        if self.scale != 1.0:
+            kernels.scale_(logits, self.scale)
+        return logits

@@ -1,0 +1,111 @@
+"""Routed experts: every token is sent to `top` of a layer's small gated feed-forwards and gets the weighted sum of
+their outputs (no biases anywhere).
+
+  z = W_router h  (float32),  s = softmax(z) over all experts (or sigmoid(z), one by one)
+  chosen = the `top` experts with the largest s + correction   (the correction steers the choice only)
+  weight_e = s_e / (sum of the chosen s + 1e-20) * scale
+  out = sum over the chosen of weight_e * expert_e(h),   expert_e(h) = W_down silu(W_gate h) * (W_up h)
+
+The last `identity` experts of the router have no tensors: their output is their input.  A shared expert (any
+registered feed-forward) may run for every token beside them, behind one sigmoid gate a token.
+
+The shapes of every launch are fixed by the number of tokens, so a step can be recorded: one kernel lists the
+(token, choice) pairs expert by expert, every expert's run filled up to whole tiles, and the two products of the
+gated unit run over those tiles, each with the weights of its tile's expert; a last kernel sums a token's
+choices in their order.  Which pairs share a tile does not enter a row's result."""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..errors import InvalidRequest
+from ..weights.spec import WeightSpec
+from .base import FEED_FORWARDS, FeedForward, PartSpec, plain
+from .linear import linear
+
+
+@FEED_FORWARDS.register("routed_experts")
+class RoutedExperts(FeedForward):
+    def __init__(self, prefix: str, width: int, experts: int, top: int, inner: int, identity: int = 0, scale: float = 1.0,
+                 score: str = "softmax", correction: bool = False, shared: PartSpec | None = None, shared_gate: bool = False,
+                 names: dict | None = None):
+        """`experts` with tensors, then `identity` without; `shared`: the feed-forward that every token passes as well
+        (its root is the leaf "shared" below this part's), `shared_gate`: behind a sigmoid gate of one number a token.
+        `names`: leaves below the part's root; "expert" is a pattern with `{}` for the expert's number."""
+        super().__init__(prefix)
+        self.width, self.experts, self.identity = int(width), int(experts), int(identity)
+        self.top, self.inner, self.scale = int(top), int(inner), float(scale)
+        if self.experts < 0 or self.identity < 0 or not 0 < self.top <= self.experts + self.identity:
+            raise InvalidRequest(f"{prefix}: {top} choices among {experts} + {identity} experts")
+        if self.experts and self.inner <= 0 or self.width <= 0:
+            raise InvalidRequest(f"{prefix}: sizes must be positive")
+        if score not in ("softmax", "sigmoid"):
+            raise InvalidRequest(f"{prefix}: router scores {score!r} are not built; softmax or sigmoid")
+        self.score, self.correction = score, bool(correction)
+        self.leaf = {"router": "router.weight", "correction": "router.correction", "expert": "experts.{}", "gate": "gate_proj.weight",
+                     "up": "up_proj.weight", "down": "down_proj.weight", "shared": "shared", "shared_gate": "shared_gate.weight"}
+        self.leaf.update(names or {})
+        self.shared = FEED_FORWARDS.build(shared, self.name(self.leaf["shared"])) if shared is not None else None
+        self.shared_gate = bool(shared_gate) and self.shared is not None
+        self.router = self.correction_values = self.gate_up = self.down = None
+
+    @property
+    def all_experts(self) -> int:
+        return self.experts + self.identity
+
+    def _expert(self, number: int, which: str) -> str:
+        return self.name(f"{self.leaf['expert'].format(number)}.{self.leaf[which]}")
+
+    def weight_specs(self):
+        n = self.leaf
+        specs = []
+        for number in range(self.experts):
+            specs += [WeightSpec(self._expert(number, "gate"), (self.inner, self.width)),
+                      WeightSpec(self._expert(number, "up"), (self.inner, self.width)),
+                      WeightSpec(self._expert(number, "down"), (self.width, self.inner))]
+        specs.append(WeightSpec(self.name(n["router"]), (self.all_experts, self.width)))
+        if self.correction:
+            specs.append(WeightSpec(self.name(n["correction"]), (self.all_experts,), "bias"))
+        if self.shared is not None:
+            specs += self.shared.weight_specs()
+        if self.shared_gate:
+            specs.append(WeightSpec(self.name(n["shared_gate"]), (1, self.width)))
+        return specs
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        n = self.leaf
+        if self.experts:
+            self.gate_up = torch.stack([torch.cat([tensors[self._expert(e, "gate")], tensors[self._expert(e, "up")]], dim=0)
+                                        for e in range(self.experts)]).contiguous()                         # [experts, 2 inner, width]
+            self.down = torch.stack([tensors[self._expert(e, "down")] for e in range(self.experts)]).contiguous()   # [experts, width, inner]
+        rows = [tensors[self.name(n["router"])]]
+        if self.shared_gate:
+            rows.append(tensors[self.name(n["shared_gate"])])
+        self.router = torch.cat(rows, dim=0).contiguous()       # the shared expert's gate is one more row of the router's product
+        self.correction_values = tensors[self.name(n["correction"])] if self.correction else None
+        if self.shared is not None:
+            self.shared.bind(tensors, runtime)
+
+    def forward(self, h, ctx):
+        h = plain(h)
+        tokens = h.shape[0]
+        device, dtype = h.device, self.runtime.dtype
+        logits = linear(h, self.router, out_dtype=torch.float32)
+        chosen = torch.empty((tokens, self.top), dtype=torch.int32, device=device)
+        weights = torch.empty((tokens, self.top), dtype=torch.float32, device=device)
+        shared_gate = torch.empty((tokens,), dtype=torch.float32, device=device) if self.shared_gate else None
+        kernels.moe_route(logits, self.correction_values, chosen, weights, shared_gate, self.all_experts, self.top, self.scale,
+                          sigmoid_scores=self.score == "sigmoid")
+        y = None
+        if self.experts:
+            y = torch.empty((tokens * self.top, self.width), dtype=dtype, device=device)
+            kernels.moe_experts(h, chosen, self.gate_up, self.down, y, self.experts)
+        shared_out = None
+        if self.shared is not None:
+            shared_out = self.shared.forward(h, ctx)
+            if self.shared_gate is False:            # no gate: the shared expert counts fully
+                shared_gate = torch.ones((tokens,), dtype=torch.float32, device=device)
+        out = torch.empty((tokens, self.width), dtype=dtype, device=device)
+        kernels.moe_combine(y, h, shared_out, chosen, weights, shared_gate, out, self.experts)
+        return out

@@ -17,23 +17,26 @@ class SwiGLU(FeedForward):
     adds_to_stream = True
     takes_prenormed = True
 
-    def __init__(self, prefix: str, width: int, inner: int, activation: str = "silu"):
+    def __init__(self, prefix: str, width: int, inner: int, activation: str = "silu", names: dict | None = None):
+        """`names`: leaves of the three tensors below the part's root, under "gate", "up" and "down"."""
         super().__init__(prefix)
         if activation != "silu":
             raise InvalidRequest(f"activation {activation!r} is not built; only silu")
         self.width, self.inner = int(width), int(inner)
+        self.leaf = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
+        self.leaf.update(names or {})
         self.gate_up = self.down = None
 
     def weight_specs(self):
-        return [WeightSpec(self.name("gate_proj.weight"), (self.inner, self.width)),
-                WeightSpec(self.name("up_proj.weight"), (self.inner, self.width)),
-                WeightSpec(self.name("down_proj.weight"), (self.width, self.inner))]
+        return [WeightSpec(self.name(self.leaf["gate"]), (self.inner, self.width)),
+                WeightSpec(self.name(self.leaf["up"]), (self.inner, self.width)),
+                WeightSpec(self.name(self.leaf["down"]), (self.width, self.inner))]
 
     BLOCK = 64     # gate rows of a 128-row weight tile of the tensor-core product; the other 64 are the up rows
 
     def bind(self, tensors, runtime):
         super().bind(tensors, runtime)
-        gate, up = tensors[self.name("gate_proj.weight")], tensors[self.name("up_proj.weight")]
+        gate, up = tensors[self.name(self.leaf["gate"])], tensors[self.name(self.leaf["up"])]
         # When serving in bfloat16 and the width allows it, blocks of 64 gate rows alternate with the 64
         # matching up rows: a weight tile of the product for few rows then holds both halves of its outputs,
         # and the product applies silu(gate) * up before it stores.
@@ -44,7 +47,7 @@ class SwiGLU(FeedForward):
                 .reshape(2 * self.inner, self.width).contiguous()
         else:
             self.gate_up = torch.cat([gate, up], dim=0).contiguous()
-        self.down = tensors[self.name("down_proj.weight")].contiguous()
+        self.down = tensors[self.name(self.leaf["down"])].contiguous()
 
     def forward(self, h, ctx, into=None):
         act = torch.empty((h.shape[0], self.inner), dtype=self.runtime.dtype, device=self.down.device)

@@ -6,9 +6,12 @@ by the same frequencies (`rotations`); kernels that have the angles at hand comp
 themselves from the frequencies of `rotation()`."""
 from __future__ import annotations
 
+import math
+
 import torch
 
 from .. import kernels
+from ..errors import InvalidRequest
 from .base import POSITION_ENCODINGS, PositionEncoding, Rotation
 
 
@@ -47,6 +50,58 @@ class RotaryPosition(PositionEncoding):
         if shared is not None:
             shared[self.shared_key] = table
         return table
+
+
+@POSITION_ENCODINGS.register("yarn_rope")
+class YarnRotaryPosition(PositionEncoding):
+    """Rotary positions on the first `rotary_dim` elements of a head (element i with i + rotary_dim / 2), with
+    frequencies stretched for contexts beyond the length the model was trained at: with d(t) = rotary_dim *
+    ln(original / (2 pi t)) / (2 ln theta), the pair that makes t turns over the original length, lo =
+    max(floor(d(fast)), 0), hi = min(ceil(d(slow)), rotary_dim - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1),
+    pair i turns by f_i / factor * ramp_i + f_i * (1 - ramp_i), f_i = theta^(-2i / rotary_dim); cosines and sines are
+    multiplied by `magnitude_slope` * ln(factor) + 1.  A factor of 1 (or none) leaves plain rotary positions.  The table
+    is made on the host in float64 and held in float32; the angles are float32."""
+
+    def __init__(self, prefix: str, rotary_dim: int, theta: float, factor: float = 1.0, original: float = 0.0, fast: float = 32.0,
+                 slow: float = 1.0, magnitude_slope: float = 0.1):
+        super().__init__(prefix)
+        self.rotary_dim, self.theta = int(rotary_dim), float(theta)
+        self.factor, self.original, self.fast, self.slow = float(factor), float(original), float(fast), float(slow)
+        self.magnitude_slope = float(magnitude_slope)
+        if self.rotary_dim % 2 or self.rotary_dim < 0 or self.theta <= 1.0:
+            raise InvalidRequest("rotary positions need an even number of elements and a base above 1")
+        self.scaled = self.factor != 1.0
+        if self.scaled and (self.factor <= 0.0 or self.original <= 0.0 or self.fast <= 0.0 or self.slow <= 0.0):
+            raise InvalidRequest("stretched rotary positions need a positive factor, original length and turn counts")
+        self.inv_freq: torch.Tensor | None = None
+
+    def frequencies(self) -> torch.Tensor:
+        dims, half = self.rotary_dim, self.rotary_dim // 2
+        plain = [self.theta ** (-2.0 * i / dims) for i in range(half)]
+        if not self.scaled:
+            return torch.tensor(plain, dtype=torch.float64)
+
+        def pair_of(turns: float) -> float:
+            return dims * math.log(self.original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.theta))
+
+        lo = max(math.floor(pair_of(self.fast)), 0)
+        hi = min(math.ceil(pair_of(self.slow)), dims - 1)
+        out = []
+        for i, f in enumerate(plain):
+            ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+            out.append(f / self.factor * ramp + f * (1.0 - ramp))
+        return torch.tensor(out, dtype=torch.float64)
+
+    @property
+    def magnitude(self) -> float:
+        return self.magnitude_slope * math.log(self.factor) + 1.0 if self.scaled else 1.0
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        self.inv_freq = self.frequencies().to(torch.float32).to(runtime.device)
+
+    def rotation(self):
+        return Rotation(self.inv_freq, self.rotary_dim, "split_half", self.magnitude)
 
 
 @POSITION_ENCODINGS.register("none")
