@@ -232,8 +232,36 @@ def hybrid_configs(size: dict, vocab: int = 32768):
     return niduvik, qwen
 
 
+def latent_configs(size: dict, vocab: int = 32768):
+    """Satedra at these layer sizes: latent attention with a latent of 256 and a rotated part of 32 elements, heads of 64
+    unrotated query/key and 64 value elements, a window of 1,024, every second layer reading the cache of the layer before
+    it; the first layer's feed-forward dense, the others 32 experts of ff / 8 with 4 chosen, 2 identity experts and a shared
+    expert of ff / 4.  Beside it the Qwen3 of equal width, heads and depth whose feed-forward is as wide as the experts a
+    token passes (4 chosen + the shared one)."""
+    w, ff = size["width"], size["ff"]
+    rot = {"base": 1000000.0, "dims": 32, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    layers = []
+    for i in range(size["layers"]):
+        mixer = {"heads": size["heads"], "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 256, "scale": 96 ** -0.5, "mask": {"size": 1024},
+                 "rot": rot}
+        if i % 2:
+            mixer["kv_from"] = i - 1
+        mlp = {"kind": "dense", "ff": ff} if i == 0 else {"kind": "moe", "expert": {"ff": ff // 8}, "shared": {"ff": ff // 4},
+                                                          "router": {"experts": 32, "identity": 2, "top": 4, "scale": 2.5}}
+        layers.append({"type": "latent_attention", "mixer": mixer, "mlp": mlp})
+    satedra = {"architecture": "Satedra", "vocab": vocab, "width": w, "norm": {"eps": 1e-5}, "logit_scale": 1.0, "layers": layers}
+    qwen = dict(QWEN3_8B, hidden_size=w, intermediate_size=4 * (ff // 8) + ff // 4, num_hidden_layers=size["layers"],
+                num_attention_heads=size["heads"], num_key_value_heads=size["kv_heads"], head_dim=128, vocab_size=vocab,
+                tie_word_embeddings=False, eos_token_id=1)
+    return satedra, qwen
+
+
+DESIGNS = {"niduvik": ("Niduvik", "Qwen3 of equal width, heads, feed-forward and depth", hybrid_configs),
+           "satedra": ("Satedra", "Qwen3 of equal width, heads and depth, its feed-forward as wide as the experts a token passes", latent_configs)}
+
+
 def hybrid_run(args, torch, peak: dict) -> dict:
-    """`--design niduvik`: prefill of one prompt and decode steps of Niduvik at layer sizes of real models, beside the
+    """`--design NAME`: prefill of one prompt and decode steps of the design at layer sizes of real models, beside the
     Qwen3 of equal sizes, both with seeded random weights in bfloat16, timed on the device; with --kernel-shares each
     model's kernels by their share of the device's time (standard error)."""
     from mini_rsglang_b200 import RuntimeConfig, kernels
@@ -242,11 +270,12 @@ def hybrid_run(args, torch, peak: dict) -> dict:
 
     size = HYBRID_SIZES[args.size]
     context, batch, prompt_len = args.context, args.batch, args.prompt
-    out = {"design": "Niduvik", "beside": "Qwen3 of equal width, heads, feed-forward and depth", "size": dict(size, name=args.size),
+    title, beside, configs = DESIGNS[args.design]
+    out = {"design": title, "beside": beside, "size": dict(size, name=args.size),
            "batch": batch, "context": context, "prompt": prompt_len, "dtype": "bf16", "data": "synthetic: seeded random weights",
            "peaks": peak}
     gen = torch.Generator().manual_seed(7)
-    for name, raw in zip(("niduvik", "qwen3"), hybrid_configs(size)):
+    for name, raw in zip((args.design, "qwen3"), configs(size)):
         config = config_from_dict(raw)
         page = 16
         pages = batch * (-(-context // page)) + 2 * (-(-prompt_len // page)) + 8
@@ -254,9 +283,9 @@ def hybrid_run(args, torch, peak: dict) -> dict:
         engine = EngineHandle.from_random(config, seed=1, dtype="bfloat16", config=limits, num_pages=pages)
         runner = engine.runner
         for entry in runner.storage.entries:
-            if entry.k is not None:
-                entry.k.normal_(0.0, 1.0)
-                entry.v.normal_(0.0, 1.0)
+            for pages_of in (entry.k, entry.v):
+                if pages_of is not None:
+                    pages_of.normal_(0.0, 1.0)
         vocab = config.vocab_size
 
         def timed(fn, repeat):
@@ -335,7 +364,7 @@ def main() -> int:
     parser.add_argument("--output-tokens", type=int, default=64, help="--continuous: generated tokens a request")
     parser.add_argument("--prefill-budget", type=int, default=512, help="--continuous: tokens a step")
     parser.add_argument("--max-running", type=int, default=64, help="--continuous: requests in flight at most")
-    parser.add_argument("--design", choices=["niduvik"], help="Niduvik beside the Qwen3 of equal sizes (prefill and decode), instead of the default measurement")
+    parser.add_argument("--design", choices=sorted(DESIGNS), help="that design beside the Qwen3 of equal sizes (prefill and decode), instead of the default measurement")
     parser.add_argument("--size", choices=sorted(HYBRID_SIZES), default="1b", help="--design: layer sizes")
     parser.add_argument("--prompt", type=int, default=2048, help="--design: tokens of the prompt")
     parser.add_argument("--kernel-shares", action="store_true",

@@ -4,8 +4,11 @@
 //                  (or sigmoid) over all experts, the `top` largest of score + correction (ties: the lower number),
 //                  their weights score / (sum of the chosen scores + 1e-20) * scale, sigmoid of the shared gate
 //   moe_align      the (token, choice) pairs that go to a routed expert, listed expert by expert, every expert's run
-//                  filled up to whole tiles of `tile` rows (-1), and the expert of every tile (-1: unused);
+//                  filled up to whole tiles of `tile` rows (-1), the expert of every tile (-1: unused) and, behind
+//                  them, the number of tiles in use (the runs are packed from the front);
 //                  experts numbered from `routed` on have no weights (they hand their input on) and get no rows
+//   moe_gather_rows  the listed pairs' input rows, in the order of the lists (zeros where a run is filled up): the
+//                  matrix that the product for many rows reads with bulk tensor copies
 //   moe_up / moe_down   the two products of the gated unit over those tiles, on the CUDA cores in float32 sums
 //                  (the 32-bit path and every size; the tensor-core version is experts_mma.cu):
 //                  act[row] = silu(W_gate[e] x) * (W_up[e] x),  y[pair] = W_down[e] act[row]
@@ -96,6 +99,7 @@ __global__ void moe_align_kernel(const int* __restrict__ chosen, int pairs, int 
             first[e] = at;
             at += (count[e] + tile - 1) / tile * tile;
         }
+        tile_expert[capacity / tile] = at / tile;
     }
     __syncthreads();
     for (int e = threadIdx.x; e < routed; e += blockDim.x)
@@ -109,12 +113,13 @@ __global__ void moe_align_kernel(const int* __restrict__ chosen, int pairs, int 
 constexpr int SIMT_TM = 32, SIMT_TN = 64, SIMT_TK = 32;
 
 // A tile of 32 rows by 64 output columns of one expert, 256 threads, each 2 rows x 4 columns.
-// GATED: the weights hold 2 * n rows an expert (gate rows, then up rows), out[row] = silu(gate) * up, the input row of
-// a listed pair is x[pair / top]; else the input row is x[its place in the list] and out is written at the pair.
+// GATED: the weights hold 2 * n rows an expert (all gate rows, then all up rows; or, with `block`, blocks of `block` gate
+// rows each followed by the matching up rows), out[row] = silu(gate) * up, the input row of a listed pair is
+// x[pair / top]; else the input row is x[its place in the list] and out is written at the pair.
 template <typename T, bool GATED>
 __global__ void __launch_bounds__(256) moe_product_simt_kernel(const T* __restrict__ x, const int* __restrict__ sorted_rows,
                                                                const int* __restrict__ tile_expert, const T* __restrict__ weight,
-                                                               T* __restrict__ out, int n, int k, int top) {
+                                                               T* __restrict__ out, int n, int k, int top, int block) {
     pdl_launch_dependents();
     pdl_wait();
     const int expert = tile_expert[blockIdx.x];
@@ -139,8 +144,10 @@ __global__ void __launch_bounds__(256) moe_product_simt_kernel(const T* __restri
         for (int idx = threadIdx.x; idx < SIMT_TN * SIMT_TK; idx += 256) {
             const int r = idx / SIMT_TK, c = idx % SIMT_TK;
             const bool in = col0 + r < n && k0 + c < k;
-            b_s[0][r][c] = in ? to_float(w[(size_t)(col0 + r) * k + k0 + c]) : 0.0f;
-            if (GATED) b_s[1][r][c] = in ? to_float(w[(size_t)(n + col0 + r) * k + k0 + c]) : 0.0f;
+            const int col = col0 + r;
+            const int gate_row = GATED && block ? col / block * 2 * block + col % block : col;
+            b_s[0][r][c] = in ? to_float(w[(size_t)gate_row * k + k0 + c]) : 0.0f;
+            if (GATED) b_s[1][r][c] = in ? to_float(w[(size_t)(gate_row + (block ? block : n)) * k + k0 + c]) : 0.0f;
         }
         __syncthreads();
 #pragma unroll 8
@@ -178,6 +185,16 @@ __global__ void __launch_bounds__(256) moe_product_simt_kernel(const T* __restri
             dst[col] = from_float<T>(v);
         }
     }
+}
+
+// One block a listed row: sixteen bytes a thread and step.
+__global__ void moe_gather_rows_kernel(const bf16* __restrict__ x, const int* __restrict__ sorted_rows, bf16* __restrict__ out, int k, int top) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int pair = sorted_rows[blockIdx.x];
+    const uint4* src = pair >= 0 ? reinterpret_cast<const uint4*>(x + (size_t)(pair / top) * k) : nullptr;
+    uint4* dst = reinterpret_cast<uint4*>(out + (size_t)blockIdx.x * k);
+    for (int i = threadIdx.x; i < k / 8; i += blockDim.x) dst[i] = src ? src[i] : make_uint4(0u, 0u, 0u, 0u);
 }
 
 // One block a token.
@@ -234,21 +251,29 @@ MRS_EXPORT int mrs_moe_align(const int* chosen, int pairs, int routed, int tile,
 }
 
 // gated != 0: x [tokens, k], weight [experts, 2 n, k], out [capacity, n]; else x [capacity, k], weight [experts, n, k],
-// out [pairs, n].  Lists in tiles of mrs_moe_simt_tile() rows.
+// out [pairs, n].  Lists in tiles of mrs_moe_simt_tile() rows.  `block` > 0 (gated): gate and up rows alternate in blocks.
 MRS_EXPORT int mrs_moe_product_simt(int is_bf16, int gated, const void* x, const int* sorted_rows, const int* tile_expert,
-                                    const void* weight, void* out, int capacity, int n, int k, int top, void* stream) {
+                                    const void* weight, void* out, int capacity, int n, int k, int top, int block, void* stream) {
     if (capacity <= 0) return 0;
-    if (capacity % SIMT_TM || n <= 0 || k <= 0 || top <= 0) return MRS_BAD_ARGUMENT;
+    if (capacity % SIMT_TM || n <= 0 || k <= 0 || top <= 0 || block < 0 || (block && n % block)) return MRS_BAD_ARGUMENT;
     const dim3 grid(capacity / SIMT_TM, (n + SIMT_TN - 1) / SIMT_TN);
 #define MRS_MOE_SIMT(T, GATED)                                                                                                   \
     MRS_LAUNCH((moe_product_simt_kernel<T, GATED>), grid, 256, 0, stream, (const T*)x, sorted_rows, tile_expert, (const T*)weight, \
-               (T*)out, n, k, top)
+               (T*)out, n, k, top, block)
     if (is_bf16) {
         if (gated) MRS_MOE_SIMT(bf16, true); else MRS_MOE_SIMT(bf16, false);
     } else {
         if (gated) MRS_MOE_SIMT(float, true); else MRS_MOE_SIMT(float, false);
     }
 #undef MRS_MOE_SIMT
+    MRS_RETURN_LAUNCH_STATUS();
+}
+
+// out [capacity, k] = the input rows x[pair / top] of the listed pairs, zeros for -1; bfloat16, k a multiple of 8.
+MRS_EXPORT int mrs_moe_gather_rows(const void* x, const int* sorted_rows, void* out, int capacity, int k, int top, void* stream) {
+    if (capacity <= 0) return 0;
+    if (k <= 0 || k % 8 || top <= 0 || (((uintptr_t)x | (uintptr_t)out) & 15)) return MRS_BAD_ARGUMENT;
+    MRS_LAUNCH(moe_gather_rows_kernel, capacity, 128, 0, stream, (const bf16*)x, sorted_rows, (bf16*)out, k, top);
     MRS_RETURN_LAUNCH_STATUS();
 }
 

@@ -33,7 +33,7 @@ __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(_
 template <bool GATED>
 __global__ void __launch_bounds__(THREADS) moe_product_mma_kernel(const bf16* __restrict__ x, const int* __restrict__ sorted_rows,
                                                                   const int* __restrict__ tile_expert, const bf16* __restrict__ weight,
-                                                                  bf16* __restrict__ out, int n, int k, int top) {
+                                                                  bf16* __restrict__ out, int n, int k, int top, int block) {
     pdl_launch_dependents();
     pdl_wait();
     const int expert = tile_expert[blockIdx.x];
@@ -64,7 +64,9 @@ __global__ void __launch_bounds__(THREADS) moe_product_mma_kernel(const bf16* __
             for (int idx = threadIdx.x; idx < BN * (BK / 8); idx += THREADS) {
                 const int r = idx / (BK / 8), c = idx % (BK / 8);
                 const bool valid = col0 + r < n && k0 + c * 8 < k;
-                const bf16* src = valid ? w + (size_t)(half * n + col0 + r) * k + k0 + c * 8 : w;
+                const int col = col0 + r;
+                const int w_row = block ? col / block * 2 * block + col % block + half * block : half * n + col;     // blocks of gate and up rows, or all gate rows first
+                const bf16* src = valid ? w + (size_t)w_row * k + k0 + c * 8 : w;
                 cp_async16(b + tile_at(r, c * 8), src, valid);
             }
         }
@@ -135,11 +137,13 @@ template <bool GATED> constexpr size_t smem_bytes() { return (size_t)(2 * BM * B
 
 MRS_EXPORT int mrs_moe_mma_tile() { return BM; }
 
-// As mrs_moe_product_simt, bfloat16 only, lists in tiles of mrs_moe_mma_tile() rows, k a multiple of 8.
+// As mrs_moe_product_simt (`block` too), bfloat16 only, lists in tiles of mrs_moe_mma_tile() rows, k a multiple of 8.
 MRS_EXPORT int mrs_moe_product_mma(int gated, const void* x, const int* sorted_rows, const int* tile_expert, const void* weight, void* out,
-                                   int capacity, int n, int k, int top, void* stream) {
+                                   int capacity, int n, int k, int top, int block, void* stream) {
     if (capacity <= 0) return 0;
-    if (capacity % BM || n <= 0 || k <= 0 || k % 8 || top <= 0 || (((uintptr_t)x | (uintptr_t)weight) & 15)) return MRS_BAD_ARGUMENT;
+    if (capacity % BM || n <= 0 || k <= 0 || k % 8 || top <= 0 || (((uintptr_t)x | (uintptr_t)weight) & 15) || block < 0 ||
+        (block && (!gated || n % block)))
+        return MRS_BAD_ARGUMENT;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(moe_product_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<true>());
@@ -151,9 +155,9 @@ MRS_EXPORT int mrs_moe_product_mma(int gated, const void* x, const int* sorted_r
     const dim3 grid(capacity / BM, (n + BN - 1) / BN);
     if (gated)
         MRS_LAUNCH(moe_product_mma_kernel<true>, grid, THREADS, smem_bytes<true>(), stream, (const bf16*)x, sorted_rows, tile_expert,
-                   (const bf16*)weight, (bf16*)out, n, k, top);
+                   (const bf16*)weight, (bf16*)out, n, k, top, block);
     else
         MRS_LAUNCH(moe_product_mma_kernel<false>, grid, THREADS, smem_bytes<false>(), stream, (const bf16*)x, sorted_rows, tile_expert,
-                   (const bf16*)weight, (bf16*)out, n, k, top);
+                   (const bf16*)weight, (bf16*)out, n, k, top, block);
     MRS_RETURN_LAUNCH_STATUS();
 }

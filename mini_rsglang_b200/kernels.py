@@ -1340,8 +1340,9 @@ _LATENT_SIGNATURES = {
     "mrs_scale": [_c_vp, ctypes.c_longlong, _c_float, _c_vp],
     "mrs_moe_route": [_c_vp, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_vp],
     "mrs_moe_align": [_c_vp, _c_int, _c_int, _c_int, _c_vp, _c_vp, _c_int, _c_vp],
-    "mrs_moe_product_simt": [_c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_vp],
-    "mrs_moe_product_mma": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_vp],
+    "mrs_moe_product_simt": [_c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_int, _c_vp],
+    "mrs_moe_gather_rows": [_c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_vp],
+    "mrs_moe_product_mma": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_int, _c_vp],
     "mrs_moe_combine": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_vp],
 }
 _latent_lib = None
@@ -1468,20 +1469,21 @@ def moe_mma_supported(x: torch.Tensor, inner: int) -> bool:
 def moe_align(chosen: torch.Tensor, routed: int, tile: int, sorted_rows: torch.Tensor, tile_expert: torch.Tensor) -> None:
     """Lists the pairs of `chosen` [tokens, top] that name one of the first `routed` experts, expert by expert, every run
     filled up with -1 to whole tiles: `sorted_rows` [capacity] the pairs (token * top + choice), `tile_expert`
-    [capacity / tile] the expert of every tile (-1: unused)."""
+    [capacity / tile + 1] the expert of every tile (-1: unused) and, last, the number of tiles in use."""
     _need(chosen, torch.int32, "chosen experts")
     _need(sorted_rows, torch.int32, "sorted rows")
-    _need(tile_expert, torch.int32, "tile experts", (sorted_rows.shape[0] // tile,))
+    _need(tile_expert, torch.int32, "tile experts", (sorted_rows.shape[0] // tile + 1,))
     _check(latent_library().mrs_moe_align(chosen.data_ptr(), chosen.numel(), routed, tile, sorted_rows.data_ptr(), tile_expert.data_ptr(),
                                           sorted_rows.shape[0], _stream()), "moe_align")
 
 
 def moe_product(x: torch.Tensor, sorted_rows: torch.Tensor, tile_expert: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
-                top: int, gated: bool, tensor_cores: bool = False) -> None:
+                top: int, gated: bool, tensor_cores: bool = False, block: int = 0) -> None:
     """One product of the experts over the lists of `moe_align`, on the CUDA cores (tiles of `moe_simt_tile()` rows) or,
-    with `tensor_cores` (bfloat16, k a multiple of 8), on the tensor cores (tiles of `moe_mma_tile()` rows).
-    `gated`: x [tokens, k], weight [experts, 2 n, k] (gate rows, then up rows), out [capacity, n] = silu(gate) * up of
-    every listed pair's token; else x [capacity, k], weight [experts, n, k], out [pairs, n] written at the pair."""
+    with `tensor_cores` (bfloat16, k a multiple of 8), with mma.sync (tiles of `moe_mma_tile()` rows).
+    `gated`: x [tokens, k], weight [experts, 2 n, k] (all gate rows, then all up rows; with `block`, blocks of that many
+    gate rows each followed by the matching up rows), out [capacity, n] = silu(gate) * up of every listed pair's token;
+    else x [capacity, k], weight [experts, n, k], out [pairs, n] written at the pair."""
     capacity = sorted_rows.shape[0]
     k = x.shape[1]
     n = out.shape[1]
@@ -1493,29 +1495,124 @@ def moe_product(x: torch.Tensor, sorted_rows: torch.Tensor, tile_expert: torch.T
     if tensor_cores:
         _need(x, torch.bfloat16, "expert input")
         _check(latent_library().mrs_moe_product_mma(int(gated), x.data_ptr(), sorted_rows.data_ptr(), tile_expert.data_ptr(),
-                                                    weight.data_ptr(), out.data_ptr(), capacity, n, k, top, _stream()), "moe_product_mma")
+                                                    weight.data_ptr(), out.data_ptr(), capacity, n, k, top, int(block) if gated else 0,
+                                                    _stream()), "moe_product_mma")
         return
     _check(latent_library().mrs_moe_product_simt(_is_bf16(x.dtype), int(gated), x.data_ptr(), sorted_rows.data_ptr(), tile_expert.data_ptr(),
-                                                 weight.data_ptr(), out.data_ptr(), capacity, n, k, top, _stream()), "moe_product_simt")
+                                                 weight.data_ptr(), out.data_ptr(), capacity, n, k, top, int(block) if gated else 0,
+                                                 _stream()), "moe_product_simt")
+
+
+MOE_TC_BLOCK = 64              # gate rows of a block in the layout of the product for many rows; the 64 matching up rows follow
+MOE_TC_MIN_PAIRS = int(os.environ.get("MRS_MOE_TC_MIN_PAIRS", "1024"))      # the variable: for measuring other crossovers
+_moe_tc_lib = None
+_moe_tc_maps: dict[tuple, tuple] = {}
+
+
+def moe_tc_library() -> ctypes.CDLL:
+    global _moe_tc_lib
+    if _moe_tc_lib is None:
+        if not torch.cuda.is_available():
+            raise BackendError("no CUDA device: the engine has no CPU path")
+        lib = specialised_kernel_library("experts_tc.cu", {})
+        lib.mrs_moe_tc_map.argtypes = [_c_vp, ctypes.c_longlong, ctypes.c_longlong, _c_int, _c_vp]
+        lib.mrs_moe_tc_map.restype = _c_int
+        lib.mrs_moe_product_tc.argtypes = [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_vp]
+        lib.mrs_moe_product_tc.restype = _c_int
+        lib.mrs_moe_tc_tile.argtypes = []
+        lib.mrs_moe_tc_tile.restype = _c_int
+        lib.mrs_moe_tc_take_error.argtypes = [ctypes.POINTER(ctypes.c_uint)]
+        lib.mrs_moe_tc_take_error.restype = _c_int
+        lib.mrs_moe_tc_error_string.argtypes = [_c_int]
+        lib.mrs_moe_tc_error_string.restype = ctypes.c_char_p
+        _moe_tc_lib = lib
+        _register_error_word("moe_product_tc", lib, "mrs_moe_tc")
+    return _moe_tc_lib
+
+
+def moe_tc_supported(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, block: int) -> bool:
+    """bfloat16, gate and up rows in blocks of 64, a width of a multiple of 8, weights on 16-byte boundaries."""
+    return (x.dtype is torch.bfloat16 and block == MOE_TC_BLOCK and x.shape[1] % 8 == 0 and down.shape[2] % MOE_TC_BLOCK == 0
+            and gate_up.data_ptr() % 16 == 0 and down.data_ptr() % 16 == 0)
+
+
+def _moe_tc_map(lib, t: torch.Tensor, rows: int, cols: int, box_rows: int, keep: bool):
+    """The address of a tensor map over `t` as a matrix [rows, cols]; kept for weights, made anew for activations."""
+    key = (t.data_ptr(), rows, cols, box_rows)
+    if keep and key in _moe_tc_maps:
+        return _moe_tc_maps[key]
+    block, address = _aligned_block(128, 64)
+    code = lib.mrs_moe_tc_map(t.data_ptr(), rows, cols, box_rows, address)
+    if code != 0:
+        raise BackendError(f"tensor map for the experts' product: {lib.mrs_moe_tc_error_string(code).decode()} (code {code})")
+    if keep:
+        _moe_tc_maps[key] = (block, address)
+    return block, address
+
+
+def moe_product_tc(x_rows: torch.Tensor, sorted_rows: torch.Tensor, tile_expert: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
+                   gated: bool) -> None:
+    """One product of the experts on the tcgen05 tensor cores over lists in tiles of 128 rows.  `x_rows` [capacity, k]: the
+    rows in the order of the lists.  `gated`: weight [experts, 2 n, k] in blocks of 64 gate and 64 up rows, out
+    [capacity, n] = silu(gate) * up; else weight [experts, n, k], out [pairs, n] written at the rows' pairs."""
+    global launch_count
+    capacity, k = x_rows.shape
+    experts, rows_each = weight.shape[0], weight.shape[1]
+    _need(x_rows, torch.bfloat16, "expert rows")
+    _need(weight, torch.bfloat16, "expert weights", (experts, rows_each, k))
+    _need(out, torch.bfloat16, "expert output")
+    _need(sorted_rows, torch.int32, "sorted rows", (capacity,))
+    _need(tile_expert, torch.int32, "tile experts", (capacity // 128 + 1,))
+    lib = moe_tc_library()
+    x_keep, x_map = _moe_tc_map(lib, x_rows, capacity, k, 128, keep=False)
+    _, w_map = _moe_tc_map(lib, weight, experts * rows_each, k, 256, keep=True)
+    launch_count += 1
+    code = lib.mrs_moe_product_tc(int(gated), x_map, w_map, tile_expert.data_ptr(), sorted_rows.data_ptr(), out.data_ptr(), capacity,
+                                  rows_each, k, sm_count(x_rows.device), _stream())
+    del x_keep
+    if code != 0:
+        raise BackendError(f"moe_product_tc: {lib.mrs_moe_tc_error_string(code).decode()} (code {code})")
+
+
+def moe_gather_rows(x: torch.Tensor, sorted_rows: torch.Tensor, out: torch.Tensor, top: int) -> None:
+    """out[place] = x[pair / top] for every listed pair, zeros where a run is filled up (bfloat16, rows of a multiple of 8)."""
+    _need(x, torch.bfloat16, "expert input")
+    _need(out, torch.bfloat16, "gathered rows", (sorted_rows.shape[0], x.shape[1]))
+    _check(latent_library().mrs_moe_gather_rows(x.data_ptr(), sorted_rows.data_ptr(), out.data_ptr(), out.shape[0], x.shape[1], top,
+                                                _stream()), "moe_gather_rows")
 
 
 def moe_experts(h: torch.Tensor, chosen: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, y: torch.Tensor, routed: int,
-                tensor_cores: bool | None = None) -> None:
+                kernel: str | None = None, block: int = 0) -> None:
     """y[token * top + choice] = W_down[e] (silu(W_gate[e] h) * (W_up[e] h)) for every pair whose expert e = chosen[token,
     choice] is one of the first `routed`; the other rows of y are left as they are.  `gate_up` [routed, 2 inner, width]
-    (gate rows, then up rows), `down` [routed, width, inner].  `tensor_cores` None: wherever the tensor-core product applies."""
+    (all gate rows, then all up rows; with `block`, blocks of that many gate rows each followed by the matching up rows),
+    `down` [routed, width, inner].  `kernel`: "simt" (CUDA cores, every size and both dtypes), "mma" (mma.sync, bfloat16,
+    sizes of a multiple of 8), "tc" (tcgen05, bfloat16, blocks of 64); None: the tcgen05 product from MOE_TC_MIN_PAIRS pairs
+    on, else mma.sync, wherever they apply."""
     tokens, top = chosen.shape
     inner = down.shape[2]
-    if tensor_cores is None:
-        tensor_cores = moe_mma_supported(h, inner)
-    tile = moe_mma_tile() if tensor_cores else moe_simt_tile()
+    if kernel is None:
+        if tokens * top >= MOE_TC_MIN_PAIRS and moe_tc_supported(h, gate_up, down, block):
+            kernel = "tc"
+        else:
+            kernel = "mma" if moe_mma_supported(h, inner) else "simt"
+    tile = {"tc": 128, "mma": moe_mma_tile(), "simt": moe_simt_tile()}[kernel]
     capacity = moe_capacity(tokens * top, routed, tile)
     sorted_rows = torch.empty((capacity,), dtype=torch.int32, device=h.device)
-    tile_expert = torch.empty((capacity // tile,), dtype=torch.int32, device=h.device)
+    tile_expert = torch.empty((capacity // tile + 1,), dtype=torch.int32, device=h.device)
     moe_align(chosen, routed, tile, sorted_rows, tile_expert)
     act = torch.empty((capacity, inner), dtype=h.dtype, device=h.device)
-    moe_product(h, sorted_rows, tile_expert, gate_up, act, top, gated=True, tensor_cores=tensor_cores)
-    moe_product(act, sorted_rows, tile_expert, down, y, top, gated=False, tensor_cores=tensor_cores)
+    if kernel == "tc":
+        if not moe_tc_supported(h, gate_up, down, block):
+            raise InvalidRequest("the experts' product for many rows needs bfloat16, blocks of 64 gate and up rows and sizes of a multiple of 8")
+        rows = torch.empty((capacity, h.shape[1]), dtype=h.dtype, device=h.device)
+        moe_gather_rows(h, sorted_rows, rows, top)
+        moe_product_tc(rows, sorted_rows, tile_expert, gate_up, act, gated=True)
+        moe_product_tc(act, sorted_rows, tile_expert, down, y, gated=False)
+        return
+    moe_product(h, sorted_rows, tile_expert, gate_up, act, top, gated=True, tensor_cores=kernel == "mma", block=block)
+    moe_product(act, sorted_rows, tile_expert, down, y, top, gated=False, tensor_cores=kernel == "mma")
 
 
 def moe_combine(y: torch.Tensor | None, h: torch.Tensor, shared_out: torch.Tensor | None, chosen: torch.Tensor, weights: torch.Tensor,

@@ -154,8 +154,11 @@ def plan_attention_tiles(ctx, group: int, wide_rows: int, kv_heads: int = 1, win
     if key in plans:
         return plans[key]
     narrow_tokens = kernels.MMA_ROWS_NARROW // group
-    if ctx.decode_tiles is not None and narrow_tokens >= 1:     # single tokens: the step's own tile list
-        plans[key] = (ctx.decode_tiles, None, ctx.max_context_len, False)
+    if ctx.decode_tiles is not None:     # single tokens: the step's own tile list, rewritten with every step of a recording
+        if narrow_tokens >= 1:
+            plans[key] = (ctx.decode_tiles, None, ctx.max_context_len, False)
+        else:                            # a group too wide for the tiles of few rows: one token a wide tile
+            plans[key] = (None, ctx.decode_tiles, ctx.max_context_len, False)
         return plans[key]
     facts = ctx.facts
     if facts is None:

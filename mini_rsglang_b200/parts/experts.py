@@ -48,6 +48,7 @@ class RoutedExperts(FeedForward):
         self.shared = FEED_FORWARDS.build(shared, self.name(self.leaf["shared"])) if shared is not None else None
         self.shared_gate = bool(shared_gate) and self.shared is not None
         self.router = self.correction_values = self.gate_up = self.down = None
+        self.block = 0
 
     @property
     def all_experts(self) -> int:
@@ -75,9 +76,18 @@ class RoutedExperts(FeedForward):
     def bind(self, tensors, runtime):
         super().bind(tensors, runtime)
         n = self.leaf
-        if self.experts:
+        # When serving in bfloat16 and the inner size allows it, blocks of 64 gate rows alternate with the 64 matching up
+        # rows: a weight tile of the product for many rows then holds both factors of its outputs.
+        self.block = kernels.MOE_TC_BLOCK if runtime.is_bf16 and self.experts and self.inner % kernels.MOE_TC_BLOCK == 0 else 0
+        if self.experts and self.block:
+            b = self.block
+            self.gate_up = torch.stack([torch.stack([tensors[self._expert(e, "gate")].view(-1, b, self.width),
+                                                     tensors[self._expert(e, "up")].view(-1, b, self.width)], dim=1)
+                                        .reshape(2 * self.inner, self.width) for e in range(self.experts)]).contiguous()
+        elif self.experts:
             self.gate_up = torch.stack([torch.cat([tensors[self._expert(e, "gate")], tensors[self._expert(e, "up")]], dim=0)
                                         for e in range(self.experts)]).contiguous()                         # [experts, 2 inner, width]
+        if self.experts:
             self.down = torch.stack([tensors[self._expert(e, "down")] for e in range(self.experts)]).contiguous()   # [experts, width, inner]
         rows = [tensors[self.name(n["router"])]]
         if self.shared_gate:
@@ -100,7 +110,7 @@ class RoutedExperts(FeedForward):
         y = None
         if self.experts:
             y = torch.empty((tokens * self.top, self.width), dtype=dtype, device=device)
-            kernels.moe_experts(h, chosen, self.gate_up, self.down, y, self.experts)
+            kernels.moe_experts(h, chosen, self.gate_up, self.down, y, self.experts, block=self.block)
         shared_out = None
         if self.shared is not None:
             shared_out = self.shared.forward(h, ctx)

@@ -49,11 +49,12 @@ def yarn_frequencies(dims: int, base: float, scaling: dict | None):
     return torch.tensor(out, dtype=torch.float64), 0.1 * math.log(factor) + 1.0
 
 
-def rotate(x, positions, frequencies, magnitude):
+def rotate(x, positions, frequencies, magnitude, angle_dtype=torch.float64):
     """x [T, ..., dims]: element i pairs with element i + dims / 2; the pair (u, v) at position p becomes
-    (u cos a - v sin a, v cos a + u sin a), a = p f_i, cos and sin times `magnitude`."""
+    (u cos a - v sin a, v cos a + u sin a), a = p f_i, cos and sin times `magnitude`.  `angle_dtype`: the precision
+    in which the table and the product p f_i are held (the design computes angles in 32-bit)."""
     half = frequencies.shape[0]
-    angle = positions.to(torch.float64)[:, None] * frequencies[None, :]            # [T, half]
+    angle = (positions.to(angle_dtype)[:, None] * frequencies.to(angle_dtype)[None, :]).to(torch.float64)          # [T, half]
     shape = (x.shape[0],) + (1,) * (x.dim() - 2) + (half,)
     cos = (torch.cos(angle) * magnitude).to(x.dtype).view(shape)
     sin = (torch.sin(angle) * magnitude).to(x.dtype).view(shape)
