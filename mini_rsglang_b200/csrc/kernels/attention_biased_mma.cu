@@ -35,9 +35,13 @@ constexpr int KV_WIDE = 32;            // keys a block in rows mode: small block
 constexpr int KV_NARROW = 64;
 constexpr float LOG2E = 1.4426950408889634f;
 
+// Elements between the rows of a [rows][W] tile in shared memory.  Rows of a multiple of 64 elements are swizzled (their
+// 16-byte pieces xor-ed with the row); the others get 16 bytes of padding, which spreads eight consecutive rows over
+// all banks (rows of 160 or 288 elements would otherwise meet in the same banks four at a time).
+template <int W> constexpr int LD = (W % 64 == 0) ? W : W + 8;
 template <int W> __device__ __forceinline__ int tile_offset(int row, int col) {      // element offset in a [rows][W] tile
     const int chunk = col >> 3;
-    return row * W + (((W % 64 == 0) ? (chunk ^ (row & 7)) : chunk) << 3) + (col & 7);
+    return row * LD<W> + (((W % 64 == 0) ? (chunk ^ (row & 7)) : chunk) << 3) + (col & 7);
 }
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
@@ -90,7 +94,7 @@ __device__ __forceinline__ void load_kv_block(bf16* dst, const bf16* __restrict_
             valid = page >= 0;
             if (valid) src = cache + (((size_t)page * nkv + kv_head) * page_size + (key & (page_size - 1))) * W + chunk * 8;
         }
-        cp_async16(dst + row * W + (((W % 64 == 0) ? (chunk ^ (row & 7)) : chunk) << 3), src, valid);
+        cp_async16(dst + tile_offset<W>(row, chunk * 8), src, valid);
     }
 }
 
@@ -103,7 +107,7 @@ __device__ __forceinline__ void load_q_tile(bf16* q_tile, const bf16* __restrict
         const bool valid = row < rows;
         const bf16* src = q;
         if (valid) src = q + ((size_t)(tile.first_token + row / group) * nq + kv_head * group + row % group) * D + chunk * 8;
-        cp_async16(q_tile + row * D + (((D % 64 == 0) ? (chunk ^ (row & 7)) : chunk) << 3), src, valid);
+        cp_async16(q_tile + tile_offset<D>(row, chunk * 8), src, valid);
     }
 }
 
@@ -217,8 +221,8 @@ __global__ void __launch_bounds__(THREADS) attention_biased_rows_kernel(
     pdl_wait();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);
-    bf16* k_tiles = q_tile + ROWS_WIDE * D;
-    bf16* v_tiles = IN_KEYS ? k_tiles : k_tiles + 2 * KV_WIDE * D;
+    bf16* k_tiles = q_tile + ROWS_WIDE * LD<D>;
+    bf16* v_tiles = IN_KEYS ? k_tiles : k_tiles + 2 * KV_WIDE * LD<D>;
     constexpr int NT = KV_WIDE / 8;
 
     const Tile tile = tiles[blockIdx.x];
@@ -260,9 +264,9 @@ __global__ void __launch_bounds__(THREADS) attention_biased_rows_kernel(
     for (int i = 0; i < blocks.count; ++i) {
         const int stage = i & 1;
         if (i + 1 < blocks.count) {
-            load_kv_block<KV_WIDE, D>(k_tiles + (stage ^ 1) * KV_WIDE * D, k_cache, pages, blocks.at(i + 1) * KV_WIDE, key_end, kv_head, nkv, page_size, page_shift);
+            load_kv_block<KV_WIDE, D>(k_tiles + (stage ^ 1) * KV_WIDE * LD<D>, k_cache, pages, blocks.at(i + 1) * KV_WIDE, key_end, kv_head, nkv, page_size, page_shift);
             if constexpr (!IN_KEYS)
-                load_kv_block<KV_WIDE, E>(v_tiles + (stage ^ 1) * KV_WIDE * E, v_cache, pages, blocks.at(i + 1) * KV_WIDE, key_end, kv_head, nkv, page_size, page_shift);
+                load_kv_block<KV_WIDE, E>(v_tiles + (stage ^ 1) * KV_WIDE * LD<E>, v_cache, pages, blocks.at(i + 1) * KV_WIDE, key_end, kv_head, nkv, page_size, page_shift);
         }
         cp_async_commit();
         cp_async_wait<1>();
@@ -275,9 +279,9 @@ __global__ void __launch_bounds__(THREADS) attention_biased_rows_kernel(
             for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) s[nt][e] = 0.0f;
-            qk_product<NT>(s, q_tile, warp * 16, k_tiles + stage * KV_WIDE * D, 0);
+            qk_product<NT>(s, q_tile, warp * 16, k_tiles + stage * KV_WIDE * LD<D>, 0);
             softmax_step<NT>(s, o, row_max, row_sum, row_pos, row_head, key0, key_end, nq, x);
-            pv_product<NT>(o, s, v_tiles + stage * KV_WIDE * VW, 0);
+            pv_product<NT>(o, s, v_tiles + stage * KV_WIDE * LD<VW>, 0);
         }
         __syncthreads();
     }
@@ -308,8 +312,8 @@ __global__ void __launch_bounds__(THREADS) attention_biased_keys_kernel(
     pdl_wait();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);
-    bf16* k_tiles = q_tile + ROWS_NARROW * D;
-    bf16* v_tiles = IN_KEYS ? k_tiles : k_tiles + 2 * KV_NARROW * D;
+    bf16* k_tiles = q_tile + ROWS_NARROW * LD<D>;
+    bf16* v_tiles = IN_KEYS ? k_tiles : k_tiles + 2 * KV_NARROW * LD<D>;
     constexpr int NT = 2;
 
     const Tile tile = tiles[blockIdx.x];
@@ -349,9 +353,9 @@ __global__ void __launch_bounds__(THREADS) attention_biased_keys_kernel(
     for (int i = block_first; i < block_last; ++i) {
         const int stage = (i - block_first) & 1;
         if (i + 1 < block_last) {
-            load_kv_block<KV_NARROW, D>(k_tiles + (stage ^ 1) * KV_NARROW * D, k_cache, pages, blocks.at(i + 1) * KV_NARROW, key_end, kv_head, nkv, page_size, page_shift);
+            load_kv_block<KV_NARROW, D>(k_tiles + (stage ^ 1) * KV_NARROW * LD<D>, k_cache, pages, blocks.at(i + 1) * KV_NARROW, key_end, kv_head, nkv, page_size, page_shift);
             if constexpr (!IN_KEYS)
-                load_kv_block<KV_NARROW, E>(v_tiles + (stage ^ 1) * KV_NARROW * E, v_cache, pages, blocks.at(i + 1) * KV_NARROW, key_end, kv_head, nkv, page_size, page_shift);
+                load_kv_block<KV_NARROW, E>(v_tiles + (stage ^ 1) * KV_NARROW * LD<E>, v_cache, pages, blocks.at(i + 1) * KV_NARROW, key_end, kv_head, nkv, page_size, page_shift);
         }
         cp_async_commit();
         cp_async_wait<1>();
@@ -363,9 +367,9 @@ __global__ void __launch_bounds__(THREADS) attention_biased_keys_kernel(
             for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) s[nt][e] = 0.0f;
-            qk_product<NT>(s, q_tile, 0, k_tiles + stage * KV_NARROW * D, warp * 16);
+            qk_product<NT>(s, q_tile, 0, k_tiles + stage * KV_NARROW * LD<D>, warp * 16);
             softmax_step<NT>(s, o, row_max, row_sum, row_pos, row_head, key0, key_end, nq, x);
-            pv_product<NT>(o, s, v_tiles + stage * KV_NARROW * VW, warp * 16);
+            pv_product<NT>(o, s, v_tiles + stage * KV_NARROW * LD<VW>, warp * 16);
         }
         __syncthreads();
     }
@@ -429,8 +433,9 @@ __global__ void __launch_bounds__(THREADS) attention_biased_combine_kernel(
     const Tile tile = tiles[blockIdx.x];
     const int kv_head = blockIdx.y, group = nq / nkv, rows = tile.tokens * group;
     const size_t base_slot = ((size_t)blockIdx.x * nkv + kv_head) * splits * ROWS_NARROW;
-    for (int idx = threadIdx.x; idx < rows * E; idx += THREADS) {
-        const int row = idx / E, col = idx % E;
+    const int row = blockIdx.z;                       // a CTA a row: few tiles still fill the GPU
+    if (row >= rows) return;
+    for (int col = threadIdx.x; col < E; col += THREADS) {
         float m = sink ? 0.0f : -CUDART_INF_F;
         for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(base_slot + (size_t)s * ROWS_NARROW + row) * 2]);
         const float base = m == -CUDART_INF_F ? 0.0f : m;
@@ -447,10 +452,10 @@ __global__ void __launch_bounds__(THREADS) attention_biased_combine_kernel(
     }
 }
 
-constexpr int KV_ROW = D + (IN_KEYS ? 0 : E);      // elements fetched a key
-constexpr size_t smem_rows = (size_t)(ROWS_WIDE * D + 2 * KV_WIDE * KV_ROW) * sizeof(bf16);
-constexpr size_t smem_keys_tiles = (size_t)(ROWS_NARROW * D + 2 * KV_NARROW * KV_ROW) * sizeof(bf16);
-constexpr size_t smem_keys_merge = (size_t)ROWS_NARROW * D * sizeof(bf16) + (size_t)(4 * ROWS_NARROW * E + 4 * ROWS_NARROW * 2) * sizeof(float);
+constexpr int KV_ROW = LD<D> + (IN_KEYS ? 0 : LD<E>);      // elements of shared memory a key
+constexpr size_t smem_rows = (size_t)(ROWS_WIDE * LD<D> + 2 * KV_WIDE * KV_ROW) * sizeof(bf16);
+constexpr size_t smem_keys_tiles = (size_t)(ROWS_NARROW * LD<D> + 2 * KV_NARROW * KV_ROW) * sizeof(bf16);
+constexpr size_t smem_keys_merge = (size_t)ROWS_NARROW * LD<D> * sizeof(bf16) + (size_t)(4 * ROWS_NARROW * E + 4 * ROWS_NARROW * 2) * sizeof(float);
 constexpr size_t smem_keys = smem_keys_tiles > smem_keys_merge ? smem_keys_tiles : smem_keys_merge;
 
 int page_shift_of(int page_size) {
@@ -500,7 +505,7 @@ MRS_EXPORT int mrs_attention_biased_mma(int narrow, const void* q, const void* k
                    (const bf16*)k_cache, (const bf16*)v_cache, positions, block_table, table_width, (const Tile*)tiles, (bf16*)out, nq, nkv,
                    page_size, shift, x, part_o, part_ml, splits);
         if (splits > 1)
-            MRS_LAUNCH(attention_biased_combine_kernel, dim3(num_tiles, nkv), THREADS, 0, stream, (const float*)part_o,
+            MRS_LAUNCH(attention_biased_combine_kernel, dim3(num_tiles, nkv, ROWS_NARROW), E < THREADS ? 32 * ((E + 31) / 32) : THREADS, 0, stream, (const float*)part_o,
                        (const float*)part_ml, (const Tile*)tiles, (bf16*)out, gate, nq, nkv, splits, sink);
     } else
         MRS_LAUNCH(attention_biased_rows_kernel, dim3(num_tiles, nkv), THREADS, smem_rows, stream, (const bf16*)q, (const bf16*)k_cache,

@@ -9,9 +9,10 @@
 //                  experts numbered from `routed` on have no weights (they hand their input on) and get no rows
 //   moe_gather_rows  the listed pairs' input rows, in the order of the lists (zeros where a run is filled up): the
 //                  matrix that the product for many rows reads with bulk tensor copies
-//   moe_up / moe_down   the two products of the gated unit over those tiles, on the CUDA cores in float32 sums
-//                  (the 32-bit path and every size; the tensor-core version is experts_mma.cu):
-//                  act[row] = silu(W_gate[e] x) * (W_up[e] x),  y[pair] = W_down[e] act[row]
+//   moe_up / moe_down   the two products of the gated unit over those tiles, on the CUDA cores in float32 sums:
+//                  act[row] = silu(W_gate[e] x) * (W_up[e] x),  y[pair] = W_down[e] act[row];
+//                  one kernel for every size (the 32-bit path), one for few rows an expert (decode steps: the
+//                  weights streamed once); the tensor-core versions are experts_mma.cu and experts_tc.cu
 //   moe_combine    out[token] = sum over its choices of weight * (y[pair] or, for an expert without weights, the
 //                  input itself) + shared gate * shared expert's output
 //
@@ -187,6 +188,104 @@ __global__ void __launch_bounds__(256) moe_product_simt_kernel(const T* __restri
     }
 }
 
+// Few rows an expert (decode steps): a tile of 4 listed rows by 32 output columns, 8 warps, each 4 columns.  The weights
+// are read once, sixteen bytes a lane and step, straight from memory (no staging: nothing is used twice), eight such
+// loads in flight a lane; the rows wait in shared memory, 2,048 columns at a time.  The kernel is bound by the weights'
+// bytes, which is what a decode step has to move.  k a multiple of 16 bytes.
+constexpr int ROWS_TM = 4, ROWS_WARPS = 8, ROWS_J = 4, ROWS_KC = 2048;
+template <typename T> struct Piece;            // sixteen bytes of T as floats
+template <> struct Piece<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+        const float4 r = *reinterpret_cast<const float4*>(p);
+        v[0] = r.x, v[1] = r.y, v[2] = r.z, v[3] = r.w;
+    }
+};
+template <> struct Piece<bf16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const bf16* p, float (&v)[8]) {
+        const uint4 r = *reinterpret_cast<const uint4*>(p);
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+            v[2 * i] = f.x, v[2 * i + 1] = f.y;
+        }
+    }
+};
+
+template <typename T, bool GATED>
+__global__ void __launch_bounds__(32 * ROWS_WARPS) moe_product_rows_kernel(const T* __restrict__ x, const int* __restrict__ sorted_rows,
+                                                                            const int* __restrict__ tile_expert, const T* __restrict__ weight,
+                                                                            T* __restrict__ out, int n, int k, int top, int block) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int expert = tile_expert[blockIdx.x];
+    if (expert < 0) return;
+    constexpr int V = Piece<T>::N, NB = GATED ? 2 : 1;
+    __shared__ __align__(16) T x_s[ROWS_TM][ROWS_KC];
+    __shared__ int row_of[ROWS_TM];
+    const int row0 = blockIdx.x * ROWS_TM;
+    if (threadIdx.x < ROWS_TM) row_of[threadIdx.x] = sorted_rows[row0 + threadIdx.x];
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const T* w = weight + (size_t)expert * NB * n * k;
+    const int col_base = blockIdx.y * (ROWS_WARPS * ROWS_J);
+    const T* w_row[ROWS_J][NB];
+#pragma unroll
+    for (int j = 0; j < ROWS_J; ++j) {
+        const int col = min(col_base + warp + ROWS_WARPS * j, n - 1);          // a column beyond the last repeats it and is not stored
+        const int gate_row = GATED && block ? col / block * 2 * block + col % block : col;
+        w_row[j][0] = w + (size_t)gate_row * k;
+        if (GATED) w_row[j][NB - 1] = w + (size_t)(gate_row + (block ? block : n)) * k;
+    }
+    float acc[ROWS_J][NB][ROWS_TM] = {};
+    for (int kc = 0; kc < k; kc += ROWS_KC) {
+        const int len = min(ROWS_KC, k - kc);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < ROWS_TM * (len / V); idx += 32 * ROWS_WARPS) {
+            const int r = idx / (len / V), c = idx % (len / V);
+            const int pair = row_of[r];
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (pair >= 0) v = *reinterpret_cast<const uint4*>(x + (size_t)(GATED ? pair / top : row0 + r) * k + kc + c * V);
+            *reinterpret_cast<uint4*>(&x_s[r][c * V]) = v;
+        }
+        __syncthreads();
+        for (int i = lane * V; i < len; i += 32 * V) {
+            float wv[ROWS_J][NB][V];
+#pragma unroll
+            for (int j = 0; j < ROWS_J; ++j)
+#pragma unroll
+                for (int b = 0; b < NB; ++b) Piece<T>::load(w_row[j][b] + kc + i, wv[j][b]);
+#pragma unroll
+            for (int r = 0; r < ROWS_TM; ++r) {
+                float xv[V];
+                Piece<T>::load(&x_s[r][i], xv);
+#pragma unroll
+                for (int j = 0; j < ROWS_J; ++j)
+#pragma unroll
+                    for (int b = 0; b < NB; ++b)
+#pragma unroll
+                        for (int e = 0; e < V; ++e) acc[j][b][r] += wv[j][b][e] * xv[e];
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < ROWS_J; ++j) {
+        const int col = col_base + warp + ROWS_WARPS * j;
+#pragma unroll
+        for (int r = 0; r < ROWS_TM; ++r) {
+            float v = warp_sum(acc[j][0][r]);
+            if (GATED) {
+                const float g = to_float(from_float<T>(v)), u = to_float(from_float<T>(warp_sum(acc[j][NB - 1][r])));   // the projections' own rounding
+                v = g / (1.0f + expf(-g)) * u;
+            }
+            const int pair = row_of[r];
+            if (lane == 0 && col < n && pair >= 0) out[(size_t)(GATED ? row0 + r : pair) * n + col] = from_float<T>(v);
+        }
+    }
+}
+
 // One block a listed row: sixteen bytes a thread and step.
 __global__ void moe_gather_rows_kernel(const bf16* __restrict__ x, const int* __restrict__ sorted_rows, bf16* __restrict__ out, int k, int top) {
     pdl_launch_dependents();
@@ -266,6 +365,29 @@ MRS_EXPORT int mrs_moe_product_simt(int is_bf16, int gated, const void* x, const
         if (gated) MRS_MOE_SIMT(float, true); else MRS_MOE_SIMT(float, false);
     }
 #undef MRS_MOE_SIMT
+    MRS_RETURN_LAUNCH_STATUS();
+}
+
+MRS_EXPORT int mrs_moe_rows_tile() { return ROWS_TM; }
+
+// As mrs_moe_product_simt for lists in tiles of mrs_moe_rows_tile() rows: few rows an expert.  k * sizeof(T) a multiple of 16,
+// x, weight on 16-byte boundaries.
+MRS_EXPORT int mrs_moe_product_rows(int is_bf16, int gated, const void* x, const int* sorted_rows, const int* tile_expert,
+                                    const void* weight, void* out, int capacity, int n, int k, int top, int block, void* stream) {
+    if (capacity <= 0) return 0;
+    if (capacity % ROWS_TM || n <= 0 || k <= 0 || k % (is_bf16 ? 8 : 4) || top <= 0 || block < 0 || (block && (!gated || n % block)) ||
+        (((uintptr_t)x | (uintptr_t)weight) & 15))
+        return MRS_BAD_ARGUMENT;
+    const dim3 grid(capacity / ROWS_TM, (n + ROWS_WARPS * ROWS_J - 1) / (ROWS_WARPS * ROWS_J));
+#define MRS_MOE_ROWS(T, GATED)                                                                                                             \
+    MRS_LAUNCH((moe_product_rows_kernel<T, GATED>), grid, 32 * ROWS_WARPS, 0, stream, (const T*)x, sorted_rows, tile_expert, (const T*)weight, \
+               (T*)out, n, k, top, block)
+    if (is_bf16) {
+        if (gated) MRS_MOE_ROWS(bf16, true); else MRS_MOE_ROWS(bf16, false);
+    } else {
+        if (gated) MRS_MOE_ROWS(float, true); else MRS_MOE_ROWS(float, false);
+    }
+#undef MRS_MOE_ROWS
     MRS_RETURN_LAUNCH_STATUS();
 }
 

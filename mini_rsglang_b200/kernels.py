@@ -1341,6 +1341,7 @@ _LATENT_SIGNATURES = {
     "mrs_moe_route": [_c_vp, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_vp],
     "mrs_moe_align": [_c_vp, _c_int, _c_int, _c_int, _c_vp, _c_vp, _c_int, _c_vp],
     "mrs_moe_product_simt": [_c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_int, _c_vp],
+    "mrs_moe_product_rows": [_c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_int, _c_vp],
     "mrs_moe_gather_rows": [_c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_vp],
     "mrs_moe_product_mma": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_int, _c_vp],
     "mrs_moe_combine": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_vp],
@@ -1362,7 +1363,7 @@ def latent_library() -> ctypes.CDLL:
             fn.restype = _c_int
         lib.mrs_moe_capacity.argtypes = [_c_int, _c_int, _c_int]
         lib.mrs_moe_capacity.restype = ctypes.c_longlong
-        for name in ("mrs_moe_simt_tile", "mrs_moe_mma_tile"):
+        for name in ("mrs_moe_simt_tile", "mrs_moe_mma_tile", "mrs_moe_rows_tile"):
             getattr(lib, name).argtypes = []
             getattr(lib, name).restype = _c_int
         _latent_lib = lib
@@ -1431,12 +1432,14 @@ def latent_prepare(proj: torch.Tensor, latent_weight: torch.Tensor | None, eps: 
 
 def moe_route(logits: torch.Tensor, correction: torch.Tensor | None, chosen: torch.Tensor, weights: torch.Tensor,
               shared_gate: torch.Tensor | None, experts: int, top: int, scale: float, sigmoid_scores: bool = False) -> None:
-    """Router logits float32 [tokens, experts (+ 1)] -> `chosen` [tokens, top] int32, the `top` experts with the largest
-    score + correction, and `weights` [tokens, top] float32, score / (sum of the chosen + 1e-20) * scale; scores are
-    the softmax (or the sigmoids) of the first `experts` columns.  With `shared_gate` [tokens] the column after them
-    is one more gate, whose sigmoid it gets."""
+    """Router logits float32 [tokens, experts (+ 1) or more] -> `chosen` [tokens, top] int32, the `top` experts with the
+    largest score + correction, and `weights` [tokens, top] float32, score / (sum of the chosen + 1e-20) * scale; scores
+    are the softmax (or the sigmoids) of the first `experts` columns.  With `shared_gate` [tokens] the column after them
+    is one more gate, whose sigmoid it gets.  Further columns are not read."""
     tokens = logits.shape[0]
-    _need(logits, torch.float32, "router logits", (tokens, experts + (1 if shared_gate is not None else 0)))
+    _need(logits, torch.float32, "router logits")
+    if logits.dim() != 2 or logits.shape[1] < experts + (1 if shared_gate is not None else 0):
+        raise InvalidRequest("moe_route: fewer logits a token than experts")
     if correction is not None:
         _need(correction, torch.float32, "router correction", (experts,))
     _need(chosen, torch.int32, "chosen experts", (tokens, top))
@@ -1461,6 +1464,16 @@ def moe_mma_tile() -> int:
     return int(latent_library().mrs_moe_mma_tile())
 
 
+def moe_rows_tile() -> int:
+    return int(latent_library().mrs_moe_rows_tile())
+
+
+def moe_rows_supported(x: torch.Tensor, inner: int) -> bool:
+    """Rows of a multiple of 16 bytes in both products."""
+    piece = 16 // x.element_size()
+    return x.shape[1] % piece == 0 and inner % piece == 0
+
+
 def moe_mma_supported(x: torch.Tensor, inner: int) -> bool:
     """bfloat16 with rows on 16-byte boundaries in both products: the width and the experts' inner size multiples of 8."""
     return x.dtype is torch.bfloat16 and x.shape[1] % 8 == 0 and inner % 8 == 0
@@ -1478,9 +1491,10 @@ def moe_align(chosen: torch.Tensor, routed: int, tile: int, sorted_rows: torch.T
 
 
 def moe_product(x: torch.Tensor, sorted_rows: torch.Tensor, tile_expert: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
-                top: int, gated: bool, tensor_cores: bool = False, block: int = 0) -> None:
-    """One product of the experts over the lists of `moe_align`, on the CUDA cores (tiles of `moe_simt_tile()` rows) or,
-    with `tensor_cores` (bfloat16, k a multiple of 8), with mma.sync (tiles of `moe_mma_tile()` rows).
+                top: int, gated: bool, kernel: str = "simt", block: int = 0) -> None:
+    """One product of the experts over the lists of `moe_align`: `kernel` "simt" (CUDA cores, tiles of `moe_simt_tile()`
+    rows, every size), "rows" (CUDA cores, few rows an expert: tiles of `moe_rows_tile()` rows, the weights streamed once;
+    rows of a multiple of 16 bytes) or "mma" (mma.sync, bfloat16, k a multiple of 8, tiles of `moe_mma_tile()` rows).
     `gated`: x [tokens, k], weight [experts, 2 n, k] (all gate rows, then all up rows; with `block`, blocks of that many
     gate rows each followed by the matching up rows), out [capacity, n] = silu(gate) * up of every listed pair's token;
     else x [capacity, k], weight [experts, n, k], out [pairs, n] written at the pair."""
@@ -1492,19 +1506,27 @@ def moe_product(x: torch.Tensor, sorted_rows: torch.Tensor, tile_expert: torch.T
     _need(out, x.dtype, "expert output")
     if (out.shape[0] if gated else x.shape[0]) != capacity:
         raise InvalidRequest("moe_product: the listed rows do not match the lists")
-    if tensor_cores:
+    if kernel == "mma":
         _need(x, torch.bfloat16, "expert input")
         _check(latent_library().mrs_moe_product_mma(int(gated), x.data_ptr(), sorted_rows.data_ptr(), tile_expert.data_ptr(),
                                                     weight.data_ptr(), out.data_ptr(), capacity, n, k, top, int(block) if gated else 0,
                                                     _stream()), "moe_product_mma")
         return
+    if kernel == "rows":
+        _check(latent_library().mrs_moe_product_rows(_is_bf16(x.dtype), int(gated), x.data_ptr(), sorted_rows.data_ptr(),
+                                                     tile_expert.data_ptr(), weight.data_ptr(), out.data_ptr(), capacity, n, k, top,
+                                                     int(block) if gated else 0, _stream()), "moe_product_rows")
+        return
+    if kernel != "simt":
+        raise InvalidRequest(f"moe_product: unknown kernel {kernel!r}")
     _check(latent_library().mrs_moe_product_simt(_is_bf16(x.dtype), int(gated), x.data_ptr(), sorted_rows.data_ptr(), tile_expert.data_ptr(),
                                                  weight.data_ptr(), out.data_ptr(), capacity, n, k, top, int(block) if gated else 0,
                                                  _stream()), "moe_product_simt")
 
 
 MOE_TC_BLOCK = 64              # gate rows of a block in the layout of the product for many rows; the 64 matching up rows follow
-MOE_TC_MIN_PAIRS = int(os.environ.get("MRS_MOE_TC_MIN_PAIRS", "1024"))      # the variable: for measuring other crossovers
+MOE_TC_MIN_PAIRS = int(os.environ.get("MRS_MOE_TC_MIN_PAIRS", "1024"))      # the variables: for measuring other crossovers
+MOE_ROWS_MAX_PAIRS = int(os.environ.get("MRS_MOE_ROWS_MAX_PAIRS", "128"))
 _moe_tc_lib = None
 _moe_tc_maps: dict[tuple, tuple] = {}
 
@@ -1587,17 +1609,20 @@ def moe_experts(h: torch.Tensor, chosen: torch.Tensor, gate_up: torch.Tensor, do
     """y[token * top + choice] = W_down[e] (silu(W_gate[e] h) * (W_up[e] h)) for every pair whose expert e = chosen[token,
     choice] is one of the first `routed`; the other rows of y are left as they are.  `gate_up` [routed, 2 inner, width]
     (all gate rows, then all up rows; with `block`, blocks of that many gate rows each followed by the matching up rows),
-    `down` [routed, width, inner].  `kernel`: "simt" (CUDA cores, every size and both dtypes), "mma" (mma.sync, bfloat16,
-    sizes of a multiple of 8), "tc" (tcgen05, bfloat16, blocks of 64); None: the tcgen05 product from MOE_TC_MIN_PAIRS pairs
-    on, else mma.sync, wherever they apply."""
+    `down` [routed, width, inner].  `kernel`: "simt" (CUDA cores, every size and both dtypes), "rows" (CUDA cores, few rows
+    an expert, rows of a multiple of 16 bytes), "mma" (mma.sync, bfloat16, sizes of a multiple of 8), "tc" (tcgen05, bfloat16,
+    blocks of 64); None: up to MOE_ROWS_MAX_PAIRS pairs "rows", from MOE_TC_MIN_PAIRS pairs on "tc", between them "mma",
+    wherever they apply, else "simt"."""
     tokens, top = chosen.shape
     inner = down.shape[2]
     if kernel is None:
-        if tokens * top >= MOE_TC_MIN_PAIRS and moe_tc_supported(h, gate_up, down, block):
+        if tokens * top <= MOE_ROWS_MAX_PAIRS and moe_rows_supported(h, inner):
+            kernel = "rows"
+        elif tokens * top >= MOE_TC_MIN_PAIRS and moe_tc_supported(h, gate_up, down, block):
             kernel = "tc"
         else:
-            kernel = "mma" if moe_mma_supported(h, inner) else "simt"
-    tile = {"tc": 128, "mma": moe_mma_tile(), "simt": moe_simt_tile()}[kernel]
+            kernel = "mma" if moe_mma_supported(h, inner) else ("rows" if moe_rows_supported(h, inner) and tokens * top <= 4 * MOE_ROWS_MAX_PAIRS else "simt")
+    tile = {"tc": 128, "mma": moe_mma_tile(), "simt": moe_simt_tile(), "rows": moe_rows_tile()}[kernel]
     capacity = moe_capacity(tokens * top, routed, tile)
     sorted_rows = torch.empty((capacity,), dtype=torch.int32, device=h.device)
     tile_expert = torch.empty((capacity // tile + 1,), dtype=torch.int32, device=h.device)
@@ -1611,8 +1636,8 @@ def moe_experts(h: torch.Tensor, chosen: torch.Tensor, gate_up: torch.Tensor, do
         moe_product_tc(rows, sorted_rows, tile_expert, gate_up, act, gated=True)
         moe_product_tc(act, sorted_rows, tile_expert, down, y, gated=False)
         return
-    moe_product(h, sorted_rows, tile_expert, gate_up, act, top, gated=True, tensor_cores=kernel == "mma", block=block)
-    moe_product(act, sorted_rows, tile_expert, down, y, top, gated=False, tensor_cores=kernel == "mma")
+    moe_product(h, sorted_rows, tile_expert, gate_up, act, top, gated=True, kernel=kernel, block=block)
+    moe_product(act, sorted_rows, tile_expert, down, y, top, gated=False, kernel=kernel)
 
 
 def moe_combine(y: torch.Tensor | None, h: torch.Tensor, shared_out: torch.Tensor | None, chosen: torch.Tensor, weights: torch.Tensor,

@@ -92,7 +92,12 @@ class RoutedExperts(FeedForward):
         rows = [tensors[self.name(n["router"])]]
         if self.shared_gate:
             rows.append(tensors[self.name(n["shared_gate"])])
-        self.router = torch.cat(rows, dim=0).contiguous()       # the shared expert's gate is one more row of the router's product
+        # the shared expert's gate is one more row of the router's product; rows of zeros fill it up to a multiple of 8, so
+        # that the float32 logits' rows start on 32-byte boundaries (the library then takes its aligned kernels)
+        count = sum(r.shape[0] for r in rows)
+        if count % 8:
+            rows.append(torch.zeros((8 - count % 8, self.width), dtype=rows[0].dtype, device=rows[0].device))
+        self.router = torch.cat(rows, dim=0).contiguous()
         self.correction_values = tensors[self.name(n["correction"])] if self.correction else None
         if self.shared is not None:
             self.shared.bind(tensors, runtime)

@@ -396,19 +396,21 @@ def test_router_choice_and_weights(experts, identity, top, scale, sigmoid):
         assert torch.equal(chosen.cpu().long(), P.route(z[:, :all_experts], w, "", {"top": top, "scale": scale})[0])
 
 
-@pytest.mark.parametrize("kernel", ["simt", "mma", "tc"])
+@pytest.mark.parametrize("kernel", ["simt", "rows", "mma", "tc"])
 @pytest.mark.parametrize("tokens,width,inner,experts,top,crowd", [(50, 72, 36, 5, 2, False), (1, 64, 24, 3, 3, False), (200, 64, 32, 4, 2, True),
                                                                   (9, 136, 200, 7, 1, False), (300, 256, 64, 12, 3, False), (700, 136, 192, 5, 2, True),
                                                                   (40, 264, 128, 3, 1, False)])
 def test_expert_products_over_the_lists(kernel, tokens, width, inner, experts, top, crowd):
-    """Both products over the expert lists against the plain gated unit, pair by pair, on the CUDA cores, with mma.sync and
-    with tcgen05: experts that nobody chose, an expert that nearly every token chose (several tiles), identity experts among
+    """Both products over the expert lists against the plain gated unit, pair by pair, on the CUDA cores (the kernel for
+    every size and the one for few rows an expert), with mma.sync and with tcgen05: experts that nobody chose, an expert that nearly every token chose (several tiles), identity experts among
     the choices (their rows of the output stay as they were), sizes that fill no tile, gate and up rows in blocks of 64 where
     the inner size allows."""
     from mini_rsglang_b200 import kernels
 
-    tensor_cores = kernel != "simt"
+    tensor_cores = kernel in ("mma", "tc")
     block = 64 if inner % 64 == 0 else 0
+    if kernel == "rows" and (width % 8 or inner % 8):
+        pytest.skip("the product for few rows takes rows of a multiple of 16 bytes")
     if kernel == "mma" and (width % 8 or inner % 8):
         pytest.skip("the tensor-core product takes rows on 16-byte boundaries")
     if kernel == "tc" and (width % 8 or not block):
