@@ -317,6 +317,60 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const T* __restrict_
     }
 }
 
+// The same, sixteen bytes a thread and step (width a multiple of 16 bytes, every row on a 16-byte boundary).
+template <typename T> struct Store16;
+template <> struct Store16<float> {
+    static __device__ __forceinline__ void store(float* p, const float (&v)[4]) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+};
+template <> struct Store16<bf16> {
+    static __device__ __forceinline__ void store(bf16* p, const float (&v)[8]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 two = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&two);
+        }
+        *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+};
+
+template <typename T>
+__global__ void moe_combine_vec_kernel(const T* __restrict__ y, const T* __restrict__ h, const T* __restrict__ shared_out,
+                                       const int* __restrict__ chosen, const float* __restrict__ weights, const float* __restrict__ shared_gate,
+                                       T* __restrict__ out, int width, int top, int routed) {
+    pdl_launch_dependents();
+    pdl_wait();
+    constexpr int V = Piece<T>::N;
+    const int t = blockIdx.x;
+    const float gate = shared_out ? shared_gate[t] : 0.0f;
+    for (int i = threadIdx.x * V; i < width; i += blockDim.x * V) {
+        float v[V] = {};
+        float own[V];
+        bool have_own = false;
+        for (int c = 0; c < top; ++c) {
+            const int pair = t * top + c;
+            const float weight = weights[pair];
+            float part[V];
+            if (chosen[pair] < routed) {
+                Piece<T>::load(y + (size_t)pair * width + i, part);
+            } else {
+                if (!have_own) Piece<T>::load(h + (size_t)t * width + i, own), have_own = true;
+#pragma unroll
+                for (int e = 0; e < V; ++e) part[e] = own[e];
+            }
+#pragma unroll
+            for (int e = 0; e < V; ++e) v[e] += weight * part[e];
+        }
+        if (shared_out) {
+            float part[V];
+            Piece<T>::load(shared_out + (size_t)t * width + i, part);
+#pragma unroll
+            for (int e = 0; e < V; ++e) v[e] += gate * part[e];
+        }
+        Store16<T>::store(out + (size_t)t * width + i, v);
+    }
+}
+
 }  // namespace
 
 MRS_EXPORT int mrs_moe_simt_tile() { return SIMT_TM; }
@@ -404,6 +458,16 @@ MRS_EXPORT int mrs_moe_combine(int is_bf16, const void* y, const void* h, const 
     if (tokens <= 0) return 0;
     if (width <= 0 || top <= 0 || (shared_out && !shared_gate)) return MRS_BAD_ARGUMENT;
     const int threads = width >= 1024 ? 256 : 128;
+    const bool aligned = (((uintptr_t)y | (uintptr_t)h | (uintptr_t)shared_out | (uintptr_t)out) & 15) == 0;
+    if (aligned && width % (is_bf16 ? 8 : 4) == 0) {
+        if (is_bf16)
+            MRS_LAUNCH(moe_combine_vec_kernel<bf16>, tokens, 128, 0, stream, (const bf16*)y, (const bf16*)h, (const bf16*)shared_out, chosen,
+                       weights, shared_gate, (bf16*)out, width, top, routed);
+        else
+            MRS_LAUNCH(moe_combine_vec_kernel<float>, tokens, 128, 0, stream, (const float*)y, (const float*)h, (const float*)shared_out,
+                       chosen, weights, shared_gate, (float*)out, width, top, routed);
+        MRS_RETURN_LAUNCH_STATUS();
+    }
     if (is_bf16)
         MRS_LAUNCH(moe_combine_kernel<bf16>, tokens, threads, 0, stream, (const bf16*)y, (const bf16*)h, (const bf16*)shared_out, chosen,
                    weights, shared_gate, (bf16*)out, width, top, routed);
