@@ -240,4 +240,7 @@ SPECIALISED_BUILDS = tuple((lambda d=d: specialised_kernel_library("attention_mm
     (lambda: specialised_kernel_library("gemm_tc.cu", {}), lambda: specialised_kernel_library("gemm_many_rows.cu", {}),
      hybrid_kernel_library, latent_kernel_library, biased_attention_library,
      lambda: specialised_kernel_library("attention_biased_mma.cu", {"MRS_HEAD_DIM": 128, "MRS_VALUE_DIM": 128}),
-     lambda: specialised_kernel_library("attention_biased_mma.cu", {"MRS_HEAD_DIM": 64, "MRS_VALUE_DIM": 32}))
+     lambda: specialised_kernel_library("attention_biased_mma.cu", {"MRS_HEAD_DIM": 64, "MRS_VALUE_DIM": 32}),
+     lambda: specialised_kernel_library("attention_biased_mma.cu", {"MRS_HEAD_DIM": 288, "MRS_VALUE_DIM": 256, "MRS_VALUES_IN_KEYS": 1}),
+     lambda: specialised_kernel_library("attention_biased_mma.cu", {"MRS_HEAD_DIM": 80, "MRS_VALUE_DIM": 64, "MRS_VALUES_IN_KEYS": 1}),
+     lambda: specialised_kernel_library("experts_tc.cu", {}))

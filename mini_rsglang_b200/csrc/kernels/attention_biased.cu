@@ -7,7 +7,7 @@
 // Keys have d elements a head and values e (the two need not agree).  Scores, softmax and sums are float32.
 // Without value pages the values are the first e elements of the key rows (a latent that serves as key and as
 // value: the cache holds one row a token).  A key on a page that was given back (-1 in the table) counts as unseen.
-// This is the CUDA-core version: float32 or bfloat16 storage, keys of up to 640 and values of up to 512 elements; it is
+// This is the CUDA-core version: float32 or bfloat16 storage, keys of up to 1,152 and values of up to 1,024 elements; it is
 // the attention of the 32-bit path and the device-side reference of the tensor-core version.
 //
 // One warp per (token, query head).  The keys a query sees are up to two runs of positions, the kept first
@@ -15,8 +15,8 @@
 // product, the warp reduces once per tile (online softmax), then all lanes add the 32 weighted value rows.
 #include "common.cuh"
 
-#define ATTN_MAX_D 640
-#define ATTN_MAX_E 512
+#define ATTN_MAX_D 1152
+#define ATTN_MAX_E 1024
 #define ATTN_WARPS 4
 
 template <typename T, int EREGS>
@@ -110,9 +110,9 @@ MRS_EXPORT int mrs_attention_biased_simt(int is_bf16, const void* q, const void*
                (const T*)v_cache, positions, seq_of_token, block_table, bias, gate, (T*)out, tokens, nq, nkv, d, e, page_size,    \
                table_width, scale, cap, window, keep_first, bias_rows, sink)
     if (is_bf16) {
-        if (e <= 128) MRS_BIASED_SIMT(bf16, 4); else if (e <= 256) MRS_BIASED_SIMT(bf16, 8); else MRS_BIASED_SIMT(bf16, 16);
+        if (e <= 128) MRS_BIASED_SIMT(bf16, 4); else if (e <= 256) MRS_BIASED_SIMT(bf16, 8); else if (e <= 512) MRS_BIASED_SIMT(bf16, 16); else MRS_BIASED_SIMT(bf16, 32);
     } else {
-        if (e <= 128) MRS_BIASED_SIMT(float, 4); else if (e <= 256) MRS_BIASED_SIMT(float, 8); else MRS_BIASED_SIMT(float, 16);
+        if (e <= 128) MRS_BIASED_SIMT(float, 4); else if (e <= 256) MRS_BIASED_SIMT(float, 8); else if (e <= 512) MRS_BIASED_SIMT(float, 16); else MRS_BIASED_SIMT(float, 32);
     }
 #undef MRS_BIASED_SIMT
     MRS_RETURN_LAUNCH_STATUS();

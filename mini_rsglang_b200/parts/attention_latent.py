@@ -50,8 +50,8 @@ class LatentAttention(Mixer):
         self.e, self.latent = int(value_dim), int(latent_dim)
         if min(self.width, self.heads, self.d, self.e, self.latent) <= 0 or self.r < 0:
             raise InvalidRequest(f"{prefix}: sizes of a latent attention must be positive")
-        if self.latent + self.r > 640 or self.latent > 512:
-            raise InvalidRequest(f"{prefix}: a latent of more than 512, or cache rows of more than 640 elements, are not built")
+        if self.latent + self.r > 1152 or self.latent > 1024:
+            raise InvalidRequest(f"{prefix}: a latent of more than 1,024, or cache rows of more than 1,152 elements, are not built")
         self.scale, self.eps, self.window = float(scale), float(eps), int(window)
         self.cache_window = self.window if cache_window is None else int(cache_window)
         if self.window < 0 or (self.cache_window and (not self.window or self.cache_window < self.window)):

@@ -298,7 +298,7 @@ def run_latent_attention(dtype, q_rows, rows, gate, R, scale, window, page, seed
 
 
 @pytest.mark.parametrize("H,R,r,window,page", [(3, 40, 8, 20, 4), (2, 44, 12, 9, 16), (5, 18, 6, 0, 8), (1, 130, 30, 1, 4), (6, 512, 64, 33, 16),
-                                               (7, 300, 33, 64, 16)])
+                                               (7, 300, 33, 64, 16), (2, 1024, 128, 40, 16)])
 def test_latent_attention_kernel_random(H, R, r, window, page):
     T_ = 150
     torch.manual_seed(H * 100 + R)
