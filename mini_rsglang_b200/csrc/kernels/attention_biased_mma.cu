@@ -213,6 +213,9 @@ __device__ __forceinline__ Blocks blocks_of(int first_pos, int key_end, int kv, 
     return b;
 }
 
+// With the values inside wide key rows (256 of them) a warp's sums alone are 128 registers and the kernel takes 240: two
+// CTAs an SM.  Held to 168 registers it spills a few words and runs three CTAs, and is slower (2,048 tokens of 16 heads,
+// rows of 288: 255 against 206 us).
 __global__ void __launch_bounds__(THREADS) attention_biased_rows_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, const int* __restrict__ positions,
     const int* __restrict__ block_table, int table_width, const Tile* __restrict__ tiles, bf16* __restrict__ out, int nq, int nkv,

@@ -497,3 +497,31 @@ def test_greedy_generation_through_the_engine(folders, dtype):
             limit = 2e-5 if dtype == "float32" else 0.02 * logits.abs().max().item()
             assert token == best or gap <= limit, f"{dtype}: engine chose {token}, plain {best}, gap {gap}"
             tokens.append(token)
+
+
+def test_command_line_generates_the_plain_tokens(folders):
+    """`bin/mini-rsglang generate` on a Satedra folder: the architecture is found by config.json, prefix sharing (on by
+    default on the command line) is switched off with a note because the model keeps windows of keys, and the tokens are
+    the plain implementation's."""
+    import subprocess
+    import sys
+
+    folder = folders[("X", False)]
+    prompt = [3, 1, 4, 1, 5, 9, 2, 6]
+    cmd = [sys.executable, os.path.join(T.ROOT, "bin", "mini-rsglang"), "--model", folder, "--dtype", "float32", "--page-size", "4",
+           "--max-seq-len", "128", "--num-pages", "40", "generate", "--token-ids", ",".join(map(str, prompt)), "--max-tokens", "12",
+           "--ignore-eos", "--json"]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr
+    assert "prefix sharing is off" in proc.stderr
+    events = [json.loads(line) for line in proc.stdout.splitlines() if line.startswith("{")]
+    tokens = [e["Token"]["token_id"] for e in events if "Token" in e]
+    done = events[-1]["Finished"]
+    assert done["reason"] == "length" and done["prompt_tokens"] == len(prompt) and done["completion_tokens"] == 12
+    config, weights = load_plain(folder)
+    sequence = list(prompt)
+    for token in tokens:
+        logits = P.forward(config, weights, sequence)[-1]
+        best = int(logits.argmax())
+        assert token == best or (logits[best] - logits[token]).item() <= 2e-5, (token, best)
+        sequence.append(token)
