@@ -247,7 +247,7 @@ def latent_configs(size: dict, vocab: int = 32768):
         if i % 2:
             mixer["kv_from"] = i - 1
         mlp = {"kind": "dense", "ff": ff} if i == 0 else {"kind": "moe", "expert": {"ff": ff // 8}, "shared": {"ff": ff // 4},
-                                                          "router": {"experts": 32, "identity": 2, "top": 4, "scale": 2.5}}
+                                                          "router": {"experts": 32, "identity": 2, "top": 4, "scale": 2.0}}
         layers.append({"type": "latent_attention", "mixer": mixer, "mlp": mlp})
     satedra = {"architecture": "Satedra", "vocab": vocab, "width": w, "norm": {"eps": 1e-5}, "logit_scale": 1.0, "layers": layers}
     qwen = dict(QWEN3_8B, hidden_size=w, intermediate_size=4 * (ff // 8) + ff // 4, num_hidden_layers=size["layers"],

@@ -82,7 +82,7 @@ def test_spec_names_runs_and_cache_windows():
     assert [m["shares_cache"] for m in mixers] == [False, True, False, True]
 
 
-@pytest.mark.parametrize("dims,base,scaling", [(8, 10000.0, STRETCH), (32, 500000.0, {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}),
+@pytest.mark.parametrize("dims,base,scaling", [(8, 10000.0, STRETCH), (48, 200000.0, {"factor": 6.0, "original": 1024, "fast": 24.0, "slow": 1.5}),
                                                (16, 100.0, {"factor": 2.0, "original": 16, "fast": 4.0, "slow": 0.5}), (6, 50.0, None), (2, 10.0, STRETCH)])
 def test_rotary_table_is_the_plain_one(dims, base, scaling):
     from mini_rsglang_b200.parts.base import POSITION_ENCODINGS, PartSpec
